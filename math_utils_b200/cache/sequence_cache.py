@@ -15,6 +15,8 @@ Layers are grouped by what their mixer keeps (its ``cache_spec``):
     share the slot's page list, so a page index means the same positions in
     every layer of the group.  A group with a window gives pages back once no
     later query can see them.
+    A mixer that keeps one row per position for all its heads (``RowCacheSpec``)
+    gets the same kind of group with pages of ``[page_tokens, width]``.
   * a ``StateGroup`` for each distinct state size: ``[n_slots, n_values]``
     float32 per cache entry, zeroed when a slot is taken.
 
@@ -29,7 +31,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.base import KVCacheSpec, StateCacheSpec
+from ..parts.base import KVCacheSpec, RowCacheSpec, StateCacheSpec
 
 PAGE_TOKENS = 64
 
@@ -105,9 +107,9 @@ class PagePool:
 @dataclass
 class KVEntryView:
     """What a mixer with a key/value cache gets for one run of its layer."""
-    pages: torch.Tensor            # [n_pages, 2, n_kv_heads, page_tokens, head_dim]
+    pages: torch.Tensor            # [n_pages, 2, n_kv_heads, page_tokens, head_dim]; rows: [n_pages, page_tokens, width]
     page_tokens: int
-    spec: KVCacheSpec
+    spec: object                   # KVCacheSpec or RowCacheSpec
     group: int                     # index into StepContext.block_tables
 
 
@@ -127,9 +129,10 @@ class KVGroup:
         self.page_tokens = page_tokens
         self.max_pages = (max_positions + page_tokens - 1) // page_tokens
         self.pool = PagePool(n_pages)
+        shape = ((n_pages, page_tokens, spec.width) if isinstance(spec, RowCacheSpec)
+                 else (n_pages, 2, spec.n_kv_heads, page_tokens, spec.head_dim))
         self.storage: Dict[int, torch.Tensor] = {
-            e: torch.zeros((n_pages, 2, spec.n_kv_heads, page_tokens, spec.head_dim), dtype=dtype, device=device)
-            for e in self.entries}
+            e: torch.zeros(shape, dtype=dtype, device=device) for e in self.entries}
         # page number of each page index of each slot; -1 where none is held
         self.table = np.full((n_slots, self.max_pages), -1, dtype=np.int32)
 
@@ -214,7 +217,7 @@ class SequenceCache:
             if spec is not None:
                 by_spec.setdefault(spec, []).append(i)
         for spec, entries in by_spec.items():
-            if isinstance(spec, KVCacheSpec):
+            if isinstance(spec, (KVCacheSpec, RowCacheSpec)):
                 g = KVGroup(len(self.kv_groups), spec, entries, self.n_pages, self.n_slots, max_positions,
                             page_tokens, dtype, device)
                 self.kv_groups.append(g)

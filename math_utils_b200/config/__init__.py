@@ -1,6 +1,7 @@
 """Typed configurations and the architecture registry."""
 from .base import (ConfigError, KeyReader, LayerSpec, ModelPlan, PartSpec,
                    ScheduleEntry, default_schedule)
+from .forisun import ForisunConfig
 from .gpt2 import Gpt2Config
 from .registry import (Architecture, architecture_for, known_architectures,
                        load_config, read_config_json, register_architecture)
@@ -12,8 +13,10 @@ register_architecture(Architecture(
     name_prefixes=("", "transformer."),
 ), replace=True)
 
+register_architecture(Architecture(names=("Forisun", "forisun"), config_class=ForisunConfig), replace=True)
+
 __all__ = [
-    "Architecture", "ConfigError", "Gpt2Config", "KeyReader", "LayerSpec", "ModelPlan",
+    "Architecture", "ConfigError", "ForisunConfig", "Gpt2Config", "KeyReader", "LayerSpec", "ModelPlan",
     "PartSpec", "ScheduleEntry", "architecture_for", "default_schedule",
     "known_architectures", "load_config", "read_config_json", "register_architecture",
 ]

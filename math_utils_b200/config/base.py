@@ -145,6 +145,7 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     stop_ids: tuple = ()
+    embedding_norm: Optional[PartSpec] = None     # a norm on the residual stream right after the embedding
     ignored_tensors: tuple = ()      # regular expressions of names a file may hold unused
 
     def validate(self) -> None:

@@ -1,7 +1,8 @@
 """One registry from an architecture's name to what builds it.
 
-``config.json`` names its architecture twice: ``model_type`` (``"gpt2"``) and
-``architectures[0]`` (``"GPT2LMHeadModel"``); either finds the entry.  The
+``config.json`` names its architecture as ``model_type`` (``"gpt2"``),
+``architectures[0]`` (``"GPT2LMHeadModel"``) or ``architecture``
+(``"Forisun"``); any of them finds the entry.  The
 reference dispatches on ``model_type`` alone through ``specRegistry`` /
 ``specFor`` and answers an unknown type with the list of known ones
 (include/ai/LocalModel.hpp:579-602, 1674-1686).
@@ -42,15 +43,16 @@ def known_architectures() -> Tuple[str, ...]:
 
 
 def architecture_for(raw: Mapping[str, Any]) -> Architecture:
-    """Looks the architecture up by ``model_type``, then ``architectures``."""
+    """Looks the architecture up by ``model_type``, then ``architectures``, then ``architecture``."""
     candidates = []
-    if isinstance(raw.get("model_type"), str):
-        candidates.append(raw["model_type"])
+    for key in ("model_type", "architecture"):
+        if isinstance(raw.get(key), str):
+            candidates.append(raw[key])
     archs = raw.get("architectures")
     if isinstance(archs, list):
         candidates.extend(a for a in archs if isinstance(a, str))
     if not candidates:
-        raise ConfigError("config.json: neither 'model_type' nor 'architectures' names an architecture")
+        raise ConfigError("config.json: none of 'model_type', 'architectures', 'architecture' names an architecture")
     for name in candidates:
         if name in _REGISTRY:
             return _REGISTRY[name]

@@ -1,6 +1,6 @@
 // Embedding gather and LayerNorm.
 //
-// embed:     x[t, :] = table[id[t], :] + (pos_table ? pos_table[pos[t], :] : 0)
+// embed:     x[t, :] = table[id[t], :] * scale + (pos_table ? pos_table[pos[t], :] : 0)
 //            -> float32 residual stream (include/ai/LocalModel.hpp:3686-3697).
 // layernorm: y = (x - mean) * rsqrt(var + eps) * gamma + beta, biased variance,
 //            two passes over the row, all in float32
@@ -12,7 +12,7 @@ namespace mu {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const TW* __restrict__ table, const TW* __restrict__ pos_table,
-                             float* __restrict__ x, int hidden) {
+                             float* __restrict__ x, int hidden, float scale) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -22,7 +22,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     float* dst = x + (long long)t * hidden;
 #pragma unroll 4
     for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
-        float v = to_float(src[d]);
+        float v = to_float(src[d]) * scale;
         if (psrc) v += to_float(psrc[d]);
         dst[d] = v;
     }
@@ -144,16 +144,16 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
 
 // table_bf16: 1 if the tables hold bfloat16, 0 for float32.
 MU_EXPORT int mu_embed(const int* ids, const int* pos, const void* table, const void* pos_table,
-                       float* x, int n_tokens, int hidden, int table_bf16, void* stream) {
+                       float* x, int n_tokens, int hidden, int table_bf16, float scale, void* stream) {
     if (n_tokens <= 0) return MU_OK;
     if (hidden <= 0 || !ids || !table || !x || (pos_table && !pos)) return MU_ERR_BAD_ARGUMENT;
     const int threads = hidden >= 256 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_bf16)
         return mu::launch_pdl(mu::embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
-                              (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
+                              (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden, scale);
     return mu::launch_pdl(mu::embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
-                          (const float*)table, (const float*)pos_table, x, hidden);
+                          (const float*)table, (const float*)pos_table, x, hidden, scale);
 }
 
 // rows: optional int32 row indices into x (n_rows of them); out_bf16 picks the output dtype.

@@ -1,0 +1,284 @@
+// A feed-forward of routed experts: router, grouping of (token, expert) pairs by expert, the experts'
+// products over each expert's rows, and the weighted sum per token.  Nothing is read back by the host,
+// so a step with these kernels can be recorded in a CUDA graph: grids are sized for the worst case and
+// blocks without work leave at once.
+//
+// mu_moe_route    z = W_r h in float32; s = sigmoid(z) (or softmax over the experts); the `top` experts with
+//                 the largest s + correction are chosen (ties: the lower index); weight = s * scale
+//                 (optionally divided by the chosen experts' sum).  One warp per token.
+// mu_moe_group    counts the pairs of each expert, gives every pair a slot so that an expert's slots are
+//                 contiguous, and lists tiles of TM slots that never straddle two experts.
+// mu_moe_gemm     for every tile: out[slot, :] = act(W1[e] x[row]) (* W2[e] x[row]) on CUDA cores, one running
+//                 sum per output over k in order, so a row's result does not depend on which rows share its
+//                 tile.  Rows of x are gathered through the slot's pair (token = pair / top) or are the slots
+//                 themselves.
+// mu_moe_combine  y[t, :] = sum over the token's pairs, in the order of its choices, of weight * out[slot, :].
+#include "common.cuh"
+
+#include <math.h>
+
+namespace mu {
+
+constexpr int MOE_TM = 32, MOE_TN = 64, MOE_TK = 32;
+
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ router,
+                                 const float* __restrict__ correction, int n_tokens, int hidden, int n_experts, int top,
+                                 float scale, int softmax, int renormalize, int* __restrict__ expert_of,
+                                 float* __restrict__ weight_of) {
+    extern __shared__ float sm[];                      // per warp: scores [n_experts], choice [n_experts]
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int t = blockIdx.x * warps + warp;
+    if (t >= n_tokens) return;
+    float* score = sm + (size_t)warp * 2 * n_experts;
+    float* choice = score + n_experts;
+    const T* row = h + (long long)t * ldh;
+    for (int e = 0; e < n_experts; ++e) {
+        const float* w = router + (long long)e * hidden;
+        float z = 0.0f;
+        for (int d = lane; d < hidden; d += 32) z += to_float(row[d]) * w[d];
+        z = warp_sum(z);
+        if (lane == 0) score[e] = z;
+    }
+    __syncwarp();
+    if (softmax) {
+        float top_z = -INFINITY, sum = 0.0f;
+        for (int e = lane; e < n_experts; e += 32) top_z = fmaxf(top_z, score[e]);
+        top_z = warp_max(top_z);
+        for (int e = lane; e < n_experts; e += 32) sum += expf(score[e] - top_z);
+        sum = warp_sum(sum);
+        for (int e = lane; e < n_experts; e += 32) score[e] = expf(score[e] - top_z) / sum;
+    } else {
+        for (int e = lane; e < n_experts; e += 32) score[e] = 1.0f / (1.0f + expf(-score[e]));
+    }
+    for (int e = lane; e < n_experts; e += 32) choice[e] = score[e] + (correction ? correction[e] : 0.0f);
+    __syncwarp();
+    float kept = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = n_experts;
+        for (int e = lane; e < n_experts; e += 32)
+            if (choice[e] > best) { best = choice[e]; arg = e; }       // first maximum of the lane's experts
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg >= n_experts) arg = 0;                                 // (not a number everywhere)
+        if (lane == 0) {
+            expert_of[(long long)t * top + k] = arg;
+            weight_of[(long long)t * top + k] = score[arg];
+            choice[arg] = -INFINITY;
+        }
+        kept += score[arg];
+        __syncwarp();
+    }
+    const float f = renormalize ? scale / kept : scale;
+    for (int k = lane; k < top; k += 32) weight_of[(long long)t * top + k] *= f;
+}
+
+// One block.  slot_of[pair], pair_of[slot], and the tile list: tile_info[3 i] = expert, [3 i + 1] = first slot,
+// [3 i + 2] = rows; n_tiles[0] = how many.
+__global__ void moe_group_kernel(const int* __restrict__ expert_of, int n_pairs, int n_experts, int* __restrict__ slot_of,
+                                 int* __restrict__ pair_of, int* __restrict__ tile_info, int* __restrict__ n_tiles) {
+    extern __shared__ int smi[];                       // count [n_experts], first [n_experts + 1], tile0 [n_experts + 1]
+    int* count = smi;
+    int* first = smi + n_experts;
+    int* tile0 = first + n_experts + 1;
+    pdl_trigger();
+    pdl_wait();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&count[expert_of[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            first[e] = at;
+            tile0[e] = tiles;
+            at += count[e];
+            tiles += (count[e] + MOE_TM - 1) / MOE_TM;
+        }
+        first[n_experts] = at;
+        tile0[n_experts] = tiles;
+        n_tiles[0] = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int n = count[e];
+        for (int i = 0, k = tile0[e]; i < n; i += MOE_TM, ++k) {
+            tile_info[3 * k] = e;
+            tile_info[3 * k + 1] = first[e] + i;
+            tile_info[3 * k + 2] = min(MOE_TM, n - i);
+        }
+        count[e] = 0;                                  // now the cursor within the expert's slots
+    }
+    __syncthreads();
+    // slots in the order of the pairs within each expert: a thread takes a run of pairs, runs in thread order
+    // would need a scan per expert; the order within an expert changes no result (every row is computed by
+    // itself), so the slots are simply drawn
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = expert_of[p];
+        const int slot = first[e] + atomicAdd(&count[e], 1);
+        slot_of[p] = slot;
+        pair_of[slot] = p;
+    }
+}
+
+__device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
+
+// GATED: out = silu(W1 x) * (W2 x); else out = W1 x.  x rows: pair_of[slot] / top if pair_of, else slot.
+template <typename T, typename TO, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ pair_of, int top,
+                const T* __restrict__ w1, const T* __restrict__ w2, long long expert_stride, long long ldw,
+                const int* __restrict__ tile_info, const int* __restrict__ n_tiles, int n, int k,
+                TO* __restrict__ out, long long ldo) {
+    __shared__ float sa[MOE_TM][MOE_TK + 1];
+    __shared__ float sw1[MOE_TN][MOE_TK + 1];
+    __shared__ float sw2[GATED ? MOE_TN : 1][MOE_TK + 1];
+    __shared__ int src_row[MOE_TM];
+    pdl_trigger();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= n_tiles[0]) return;
+    const int e = tile_info[3 * tile], slot0 = tile_info[3 * tile + 1], rows = tile_info[3 * tile + 2];
+    const int n0 = blockIdx.y * MOE_TN;
+    const T* w1e = w1 + (long long)e * expert_stride;
+    const T* w2e = GATED ? w2 + (long long)e * expert_stride : nullptr;
+    if (threadIdx.x < MOE_TM) {
+        const int r = threadIdx.x;
+        src_row[r] = r < rows ? (pair_of ? pair_of[slot0 + r] / top : slot0 + r) : -1;
+    }
+    __syncthreads();
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;     // rows 2 ty, 2 ty + 1; columns tx + 16 j
+    float a1[2][4] = {}, a2[2][4] = {};
+    for (int k0 = 0; k0 < k; k0 += MOE_TK) {
+        for (int i = threadIdx.x; i < MOE_TM * MOE_TK; i += 256) {
+            const int r = i / MOE_TK, c = i % MOE_TK;
+            const int row = src_row[r];
+            sa[r][c] = (row >= 0 && k0 + c < k) ? to_float(x[(long long)row * ldx + k0 + c]) : 0.0f;
+        }
+        for (int i = threadIdx.x; i < MOE_TN * MOE_TK; i += 256) {
+            const int r = i / MOE_TK, c = i % MOE_TK;
+            const bool in = n0 + r < n && k0 + c < k;
+            sw1[r][c] = in ? to_float(w1e[(long long)(n0 + r) * ldw + k0 + c]) : 0.0f;
+            if (GATED) sw2[r][c] = in ? to_float(w2e[(long long)(n0 + r) * ldw + k0 + c]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int c = 0; c < MOE_TK; ++c) {
+            const float x0 = sa[2 * ty][c], x1 = sa[2 * ty + 1][c];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float u = sw1[tx + 16 * j][c];
+                a1[0][j] += x0 * u;
+                a1[1][j] += x1 * u;
+                if (GATED) {
+                    const float v = sw2[tx + 16 * j][c];
+                    a2[0][j] += x0 * v;
+                    a2[1][j] += x1 * v;
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = 2 * ty + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int col = n0 + tx + 16 * j;
+            if (col >= n) continue;
+            const float v = GATED ? silu(a1[i][j]) * a2[i][j] : a1[i][j];
+            out[(long long)(slot0 + r) * ldo + col] = from_float<TO>(v);
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, long long ldy, const int* __restrict__ slot_of,
+                                   const float* __restrict__ weight_of, int top, int width, float* __restrict__ out,
+                                   long long ldo) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float v = 0.0f;
+        for (int k = 0; k < top; ++k)
+            v += weight_of[(long long)t * top + k] * y[(long long)slot_of[(long long)t * top + k] * ldy + d];
+        out[(long long)t * ldo + d] = v;
+    }
+}
+
+}  // namespace mu
+
+MU_EXPORT int mu_moe_tile_rows() { return mu::MOE_TM; }
+
+MU_EXPORT int mu_moe_route(const void* h, long long ldh, int h_bf16, const float* router, const float* correction,
+                           int n_tokens, int hidden, int n_experts, int top, float scale, int softmax, int renormalize,
+                           int* expert_of, float* weight_of, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!h || !router || !expert_of || !weight_of || hidden <= 0 || n_experts <= 0 || top <= 0 || top > n_experts)
+        return MU_ERR_BAD_ARGUMENT;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * 2 * n_experts * sizeof(float);
+    if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((n_tokens + warps - 1) / warps), block(warps * 32);
+    if (h_bf16)
+        return mu::launch_pdl(mu::moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, 1, (const __nv_bfloat16*)h, ldh,
+                              router, correction, n_tokens, hidden, n_experts, top, scale, softmax, renormalize,
+                              expert_of, weight_of);
+    return mu::launch_pdl(mu::moe_route_kernel<float>, grid, block, smem, s, 1, (const float*)h, ldh, router, correction,
+                          n_tokens, hidden, n_experts, top, scale, softmax, renormalize, expert_of, weight_of);
+}
+
+// tile_info needs 3 * (n_pairs / tile_rows + n_experts) ints.
+MU_EXPORT int mu_moe_group(const int* expert_of, int n_pairs, int n_experts, int* slot_of, int* pair_of, int* tile_info,
+                           int* n_tiles, void* stream) {
+    if (n_pairs <= 0) return MU_OK;
+    if (!expert_of || !slot_of || !pair_of || !tile_info || !n_tiles || n_experts <= 0) return MU_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(3 * n_experts + 2) * sizeof(int);
+    if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
+    return mu::launch_pdl(mu::moe_group_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, 1, expert_of, n_pairs,
+                          n_experts, slot_of, pair_of, tile_info, n_tiles);
+}
+
+// w1 (and w2 when gated): [n_experts][n][k] with row stride ldw and expert stride `expert_stride` elements.
+// max_tiles: the bound the grid is sized for (n_pairs / tile_rows + n_experts covers every grouping).
+MU_EXPORT int mu_moe_gemm(const void* x, long long ldx, const int* pair_of, int top, const void* w1, const void* w2,
+                          long long expert_stride, long long ldw, const int* tile_info, const int* n_tiles,
+                          int max_tiles, int n, int k, void* out, long long ldo, int is_bf16, int out_bf16,
+                          void* stream) {
+    if (max_tiles <= 0) return MU_OK;
+    if (!x || !w1 || !tile_info || !n_tiles || !out || n <= 0 || k <= 0 || (pair_of && top <= 0))
+        return MU_ERR_BAD_ARGUMENT;
+    if (is_bf16 != out_bf16 && !(is_bf16 && !out_bf16)) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(max_tiles, (n + mu::MOE_TN - 1) / mu::MOE_TN), block(256);
+    typedef __nv_bfloat16 bf;
+#define MU_MOE(T, TO, G)                                                                                             \
+    return mu::launch_pdl(mu::moe_gemm_kernel<T, TO, G>, grid, block, 0, s, 1, (const T*)x, ldx, pair_of, top,        \
+                          (const T*)w1, (const T*)w2, expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo)
+    if (w2) {
+        if (is_bf16 && out_bf16) MU_MOE(bf, bf, true);
+        if (is_bf16) MU_MOE(bf, float, true);
+        MU_MOE(float, float, true);
+    }
+    if (is_bf16 && out_bf16) MU_MOE(bf, bf, false);
+    if (is_bf16) MU_MOE(bf, float, false);
+    MU_MOE(float, float, false);
+#undef MU_MOE
+}
+
+MU_EXPORT int mu_moe_combine(const float* y, long long ldy, const int* slot_of, const float* weight_of, int n_tokens,
+                             int top, int width, float* out, long long ldo, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!y || !slot_of || !weight_of || !out || top <= 0 || width <= 0) return MU_ERR_BAD_ARGUMENT;
+    return mu::launch_pdl(mu::moe_combine_kernel, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0,
+                          (cudaStream_t)stream, 1, y, ldy, slot_of, weight_of, top, width, out, ldo);
+}

@@ -1,0 +1,115 @@
+// Norms without a mean, and a sigmoid gate.
+//
+// dynamic_tanh:  y = tanh(alpha * x) * w + b          (no statistics of the row; alpha a scalar on the device)
+//                with ADD the result is added to what y holds (a sublayer's normed output joining the
+//                float32 residual stream); input always float32, output float32 or the compute dtype.
+// rms_norm:      y = x / sqrt(mean(x^2) + eps) * w, statistics in float32.
+// sigmoid_gate:  o *= 1 / (1 + exp(-g)), element by element, in float32.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace mu {
+
+template <typename TO, bool ADD>
+__global__ void dynamic_tanh_kernel(const float* __restrict__ x, long long ldx, const int* __restrict__ rows,
+                                    const float* __restrict__ w, const float* __restrict__ b,
+                                    const float* __restrict__ alpha, TO* __restrict__ y, long long ldy, int hidden) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float a = alpha[0];
+    const float* src = x + (rows ? (long long)rows[r] : (long long)r) * ldx;
+    TO* dst = y + (long long)r * ldy;
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        float v = tanhf(a * src[d]) * w[d] + (b ? b[d] : 0.0f);
+        if (ADD) v += to_float(dst[d]);
+        dst[d] = from_float<TO>(v);
+    }
+}
+
+template <typename TI, typename TO>
+__global__ void rms_norm_kernel(const TI* __restrict__ x, long long ldx, const float* __restrict__ w,
+                                TO* __restrict__ y, long long ldy, int n, float eps) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const TI* src = x + (long long)blockIdx.x * ldx;
+    TO* dst = y + (long long)blockIdx.x * ldy;
+    float s = 0.0f;
+    for (int d = threadIdx.x; d < n; d += blockDim.x) {
+        const float v = to_float(src[d]);
+        s += v * v;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)n + eps);
+    for (int d = threadIdx.x; d < n; d += blockDim.x) dst[d] = from_float<TO>(to_float(src[d]) * inv * w[d]);
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ o, long long ldo, const T* __restrict__ g, long long ldg,
+                                    int n_rows, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)n_rows * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / width;
+        const int c = (int)(i % width);
+        const float z = to_float(g[r * ldg + c]);
+        const float v = to_float(o[r * ldo + c]) / (1.0f + expf(-z));
+        o[r * ldo + c] = from_float<T>(v);
+    }
+}
+
+}  // namespace mu
+
+// y (+)= tanh(alpha x) w + b for n_rows rows (optionally the rows that `rows` picks from x).
+// out_bf16: y is bfloat16 (else float32); add: accumulate into y (float32 only).
+MU_EXPORT int mu_dynamic_tanh(const float* x, long long ldx, const int* rows, const float* w, const float* b,
+                              const float* alpha, void* y, long long ldy, int n_rows, int hidden, int out_bf16,
+                              int add, void* stream) {
+    if (n_rows <= 0) return MU_OK;
+    if (hidden <= 0 || !x || !w || !alpha || !y || (add && out_bf16)) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_rows), block(hidden >= 1024 ? 256 : 128);
+    if (out_bf16)
+        return mu::launch_pdl(mu::dynamic_tanh_kernel<__nv_bfloat16, false>, grid, block, 0, s, 1, x, ldx, rows, w, b,
+                              alpha, (__nv_bfloat16*)y, ldy, hidden);
+    if (add)
+        return mu::launch_pdl(mu::dynamic_tanh_kernel<float, true>, grid, block, 0, s, 1, x, ldx, rows, w, b, alpha,
+                              (float*)y, ldy, hidden);
+    return mu::launch_pdl(mu::dynamic_tanh_kernel<float, false>, grid, block, 0, s, 1, x, ldx, rows, w, b, alpha,
+                          (float*)y, ldy, hidden);
+}
+
+// y = rms_norm(x) * w over rows of n values; x and y are bfloat16 or float32 as the flags say.
+MU_EXPORT int mu_rms_norm(const void* x, long long ldx, int x_bf16, const float* w, void* y, long long ldy,
+                          int y_bf16, int n_rows, int n, float eps, void* stream) {
+    if (n_rows <= 0) return MU_OK;
+    if (n <= 0 || !x || !w || !y) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_rows), block(n >= 1024 ? 256 : 128);
+    typedef __nv_bfloat16 bf;
+    if (x_bf16 && y_bf16)
+        return mu::launch_pdl(mu::rms_norm_kernel<bf, bf>, grid, block, 0, s, 1, (const bf*)x, ldx, w, (bf*)y, ldy, n, eps);
+    if (x_bf16)
+        return mu::launch_pdl(mu::rms_norm_kernel<bf, float>, grid, block, 0, s, 1, (const bf*)x, ldx, w, (float*)y, ldy, n, eps);
+    if (y_bf16)
+        return mu::launch_pdl(mu::rms_norm_kernel<float, bf>, grid, block, 0, s, 1, (const float*)x, ldx, w, (bf*)y, ldy, n, eps);
+    return mu::launch_pdl(mu::rms_norm_kernel<float, float>, grid, block, 0, s, 1, (const float*)x, ldx, w, (float*)y, ldy, n, eps);
+}
+
+// o[r, c] *= sigmoid(g[r, c]).
+MU_EXPORT int mu_sigmoid_gate(void* o, long long ldo, const void* g, long long ldg, int n_rows, int width, int is_bf16,
+                              void* stream) {
+    if (n_rows <= 0 || width <= 0) return MU_OK;
+    if (!o || !g) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)n_rows * width;
+    const dim3 grid((unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256)), block(256);
+    if (is_bf16)
+        return mu::launch_pdl(mu::sigmoid_gate_kernel<__nv_bfloat16>, grid, block, 0, s, 1, (__nv_bfloat16*)o, ldo,
+                              (const __nv_bfloat16*)g, ldg, n_rows, width);
+    return mu::launch_pdl(mu::sigmoid_gate_kernel<float>, grid, block, 0, s, 1, (float*)o, ldo, (const float*)g, ldg,
+                          n_rows, width);
+}

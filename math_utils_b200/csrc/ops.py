@@ -49,7 +49,7 @@ _c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 
 _SIGNATURES = {
     "mu_copy_async": [_c_p, _c_p, _c_ll, _c_p],
-    "mu_embed": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p],
+    "mu_embed": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p],
     "mu_layernorm": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p],
     "mu_gemm_simt": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                      _c_int, _c_int, _c_int, _c_p],
@@ -81,6 +81,22 @@ _SIGNATURES = {
                             _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
                                _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p],
+    "mu_dynamic_tanh": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p],
+    "mu_rms_norm": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p],
+    "mu_sigmoid_gate": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
+    "mu_rotary": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_f, _c_int, _c_int, _c_int,
+                  _c_int, _c_p],
+    "mu_latent_append": [_c_p, _c_ll, _c_p, _c_f, _c_p, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int,
+                         _c_int, _c_p, _c_int, _c_p],
+    "mu_latent_attention": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int,
+                            _c_p, _c_ll, _c_p, _c_p, _c_int, _c_p],
+    "mu_moe_route": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p,
+                     _c_p],
+    "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p],
+    "mu_moe_gemm": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll,
+                    _c_int, _c_int, _c_p],
+    "mu_moe_combine": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_p],
+    "mu_moe_tile_rows": [],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int,
                   _c_p, _c_p, _c_p],
 }
@@ -205,8 +221,8 @@ def zeroed_workspace(name: str, device, n_bytes: int) -> torch.Tensor:
 
 # ------------------------------------------------------------------ elementwise
 def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Tensor,
-          pos_table: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = table[ids[t]] + pos_table[positions[t]] as float32 [T, hidden]."""
+          pos_table: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale + pos_table[positions[t]] as float32 [T, hidden]."""
     _need_cuda(ids, positions, table, pos_table)
     _i32(ids, "ids"); _i32(positions, "positions")
     n, hidden = ids.numel(), table.shape[1]
@@ -217,7 +233,8 @@ def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Ten
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _check(library().mu_embed(_ptr(ids), _ptr(positions),
-                              _ptr(table), _ptr(pos_table), _ptr(out), n, hidden, _is_bf16(table), _stream()),
+                              _ptr(table), _ptr(pos_table), _ptr(out), n, hidden, _is_bf16(table), float(scale),
+                              _stream()),
            "embed")
     return out
 
@@ -238,6 +255,179 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor]
         out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
     _check(library().mu_layernorm(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), n, hidden,
                                   float(eps), _is_bf16(out), _stream()), ("layernorm(hidden={})", hidden))
+    return out
+
+
+def dynamic_tanh(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], alpha: torch.Tensor,
+                 out_dtype: Optional[torch.dtype] = None, rows: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, add: bool = False) -> torch.Tensor:
+    """tanh(alpha x) * weight + bias of float32 rows (optionally the rows that ``rows`` picks); ``alpha`` is a
+    float32 scalar on the device.  With ``add`` the result is added to the float32 ``out``."""
+    _need_cuda(x, weight, bias, alpha, rows, out)
+    _i32(rows, "rows")
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("dynamic_tanh input must be float32 [rows, hidden] with unit inner stride")
+    for t in (weight, bias, alpha):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError("dynamic_tanh parameters must be contiguous float32")
+    hidden = x.shape[1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if out is None:
+        if add:
+            raise KernelError("dynamic_tanh(add=True) needs the tensor to add to")
+        out = torch.empty((n, hidden), dtype=out_dtype or torch.float32, device=x.device)
+    if out.shape != (n, hidden) or out.stride(1) != 1 or (add and out.dtype != torch.float32):
+        raise KernelError("dynamic_tanh output has the wrong shape, stride or dtype")
+    _check(library().mu_dynamic_tanh(_ptr(x), x.stride(0), _ptr(rows), _ptr(weight), _ptr(bias), _ptr(alpha), _ptr(out),
+                                     out.stride(0), n, hidden, _is_bf16(out), int(add), _stream()),
+           ("dynamic_tanh(hidden={})", hidden))
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: Optional[torch.dtype] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight over each row ([rows, n] views with unit inner stride, bfloat16 or
+    float32); statistics in float32."""
+    _need_cuda(x, weight, out)
+    if x.dim() != 2 or x.stride(1) != 1 or weight.dtype != torch.float32 or weight.numel() != x.shape[1]:
+        raise KernelError("rms_norm takes [rows, n] with unit inner stride and a float32 weight of n values")
+    if out is None:
+        out = torch.empty(tuple(x.shape), dtype=out_dtype or x.dtype, device=x.device)
+    if out.shape != x.shape or out.stride(1) != 1:
+        raise KernelError("rms_norm output has the wrong shape or stride")
+    _check(library().mu_rms_norm(_ptr(x), x.stride(0), _is_bf16(x), _ptr(weight), _ptr(out), out.stride(0), _is_bf16(out),
+                                 x.shape[0], x.shape[1], float(eps), _stream()), ("rms_norm(n={})", x.shape[1]))
+    return out
+
+
+def sigmoid_gate(o: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """o *= sigmoid(g) in place ([rows, width] views of one dtype with unit inner stride), in float32."""
+    _need_cuda(o, g)
+    if o.shape != g.shape or o.dtype != g.dtype or o.dim() != 2 or o.stride(1) != 1 or g.stride(1) != 1:
+        raise KernelError("sigmoid_gate takes two [rows, width] views of one dtype with unit inner stride")
+    _check(library().mu_sigmoid_gate(_ptr(o), o.stride(0), _ptr(g), g.stride(0), o.shape[0], o.shape[1], _is_bf16(o),
+                                     _stream()), "sigmoid_gate")
+    return o
+
+
+def rotary(x: torch.Tensor, out: torch.Tensor, tok_pos: torch.Tensor, freqs: torch.Tensor, magnitude: float,
+           n_heads: int, dims: int, width: int, x_head_stride: int, out_head_stride: int) -> torch.Tensor:
+    """Rotates, for every token (row) and head, ``dims`` entries of the head's slice of ``width`` entries: entry i
+    with entry i + dims/2 by the angle position * freqs[i], cos and sin times ``magnitude``; entries past ``dims``
+    are copied.  ``x`` and ``out`` are views whose first element is head 0's first entry; they may be the same."""
+    _need_cuda(x, out, tok_pos, freqs)
+    _i32(tok_pos, "tok_pos")
+    if freqs.dtype != torch.float32 or freqs.numel() != dims // 2 or dims % 2:
+        raise KernelError("rotary wants dims / 2 float32 frequencies")
+    _check(library().mu_rotary(_ptr(x), x.stride(0), int(x_head_stride), _is_bf16(x), _ptr(out), out.stride(0),
+                               int(out_head_stride), _is_bf16(out), _ptr(tok_pos), _ptr(freqs), float(magnitude),
+                               x.shape[0], int(n_heads), int(dims), int(width), _stream()), ("rotary(dims={})", dims))
+    return out
+
+
+def latent_append(dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, freqs: torch.Tensor, magnitude: float,
+                  rot_dims: int, kv_rank: int, rot_dim: int, tok_pos, tok_seq, block_table: torch.Tensor,
+                  page_tokens: int, rows: torch.Tensor) -> None:
+    """Per token: the RMS norm of the first ``kv_rank`` values of ``dkv`` and the rotation of the last ``rot_dim``
+    go to the token's row of the latent cache ``rows`` [pages, page_tokens, kv_rank + rot_dim]."""
+    _need_cuda(dkv, norm_weight, freqs, tok_pos, tok_seq, block_table, rows)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    if dkv.dtype != rows.dtype or dkv.stride(1) != 1 or dkv.shape[1] != kv_rank + rot_dim or not rows.is_contiguous():
+        raise KernelError("latent_append: the projection and the cache must share a dtype and the row width")
+    if rows.shape[1] != page_tokens or rows.shape[2] != kv_rank + rot_dim:
+        raise KernelError("latent_append: the cache is not [pages, page_tokens, kv_rank + rot_dim]")
+    _check(library().mu_latent_append(_ptr(dkv), dkv.stride(0), _ptr(norm_weight), float(eps), _ptr(freqs),
+                                      float(magnitude), int(rot_dims), int(kv_rank), int(rot_dim), _ptr(tok_pos),
+                                      _ptr(tok_seq), _ptr(block_table), block_table.shape[1], int(page_tokens),
+                                      dkv.shape[0], _ptr(rows), _is_bf16(rows), _stream()), "latent_append")
+
+
+def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Tensor, page_tokens: int, tok_pos, tok_seq,
+                     n_heads: int, kv_rank: int, scale: float, out: torch.Tensor, n_splits: int = 1,
+                     part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of float32 queries [T, n_heads, width] over the latent rows 0..position of each token's sequence;
+    ``out`` [T, n_heads * kv_rank] receives the weighted sums of the rows' first ``kv_rank`` values."""
+    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, part_o, part_ml)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    width = rows.shape[2]
+    n_tokens = q.shape[0]
+    if q.dtype != torch.float32 or not q.is_contiguous() or q.numel() != n_tokens * n_heads * width:
+        raise KernelError("latent_attention queries must be contiguous float32 [T, heads, width]")
+    if out.dtype != rows.dtype or out.stride(1) != 1 or out.shape[1] != n_heads * kv_rank or not rows.is_contiguous():
+        raise KernelError("latent_attention output must be [T, heads * kv_rank] in the cache's dtype")
+    if n_splits > 1:
+        need = n_tokens * n_heads * n_splits
+        if (part_o is None or part_ml is None or part_o.numel() < need * kv_rank or part_ml.numel() < need * 2
+                or part_o.dtype != torch.float32 or part_ml.dtype != torch.float32):
+            raise KernelError("split attention needs float32 scratch for its partial results")
+    _check(library().mu_latent_attention(_ptr(q), _ptr(rows), _ptr(block_table), block_table.shape[1], int(page_tokens),
+                                         _ptr(tok_pos), _ptr(tok_seq), n_tokens, int(n_heads), int(kv_rank), int(width),
+                                         float(scale), int(n_splits), _ptr(out), out.stride(0), _ptr(part_o),
+                                         _ptr(part_ml), _is_bf16(rows), _stream()),
+           ("latent_attention(heads={}, kv_rank={}, width={})", n_heads, kv_rank, width),
+           launches=2 if n_splits > 1 else 1)
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+def moe_tile_rows() -> int:
+    return int(library().mu_moe_tile_rows())
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
+              expert_of: torch.Tensor, weight_of: torch.Tensor, softmax: bool = False, renormalize: bool = False) -> None:
+    """Router of a feed-forward of experts: logits in float32 from the rows of ``h``, sigmoid (or softmax) scores,
+    the ``top`` experts by score + correction into ``expert_of`` [T, top] int32, score * scale into ``weight_of``."""
+    _need_cuda(h, router, correction, expert_of, weight_of)
+    n_experts, hidden = router.shape
+    if router.dtype != torch.float32 or not router.is_contiguous() or h.shape[1] != hidden or h.stride(1) != 1:
+        raise KernelError("moe_route takes rows [T, hidden] and a contiguous float32 router [experts, hidden]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != n_experts):
+        raise KernelError("moe_route: the correction is one float32 per expert")
+    _i32(expert_of, "expert_of")
+    _check(library().mu_moe_route(_ptr(h), h.stride(0), _is_bf16(h), _ptr(router), _ptr(correction), h.shape[0], hidden,
+                                  n_experts, int(top), float(scale), int(softmax), int(renormalize), _ptr(expert_of),
+                                  _ptr(weight_of), _stream()), ("moe_route(experts={}, top={})", n_experts, top))
+
+
+def moe_group(expert_of: torch.Tensor, n_experts: int, slot_of: torch.Tensor, pair_of: torch.Tensor,
+              tile_info: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """Groups the (token, expert) pairs by expert: a slot per pair, and the list of row tiles per expert."""
+    _need_cuda(expert_of, slot_of, pair_of, tile_info, n_tiles)
+    for t, name in ((expert_of, "expert_of"), (slot_of, "slot_of"), (pair_of, "pair_of"), (tile_info, "tile_info"),
+                    (n_tiles, "n_tiles")):
+        _i32(t, name)
+    _check(library().mu_moe_group(_ptr(expert_of), expert_of.numel(), int(n_experts), _ptr(slot_of), _ptr(pair_of),
+                                  _ptr(tile_info), _ptr(n_tiles), _stream()), "moe_group")
+
+
+def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: torch.Tensor, w2: Optional[torch.Tensor],
+             tile_info: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, out: torch.Tensor) -> torch.Tensor:
+    """out[slot] = W1[e] x[row] (or silu(W1[e] x[row]) * W2[e] x[row] with ``w2``) for every slot of every expert e;
+    ``w1``/``w2`` [experts, n, k]; rows of ``x`` by the slot's token (``pair_of``) or by slot."""
+    _need_cuda(x, pair_of, w1, w2, tile_info, n_tiles, out)
+    if w1.dim() != 3 or not w1.is_contiguous() or w1.dtype != x.dtype or x.stride(1) != 1 or x.shape[1] != w1.shape[2]:
+        raise KernelError("moe_gemm takes rows [*, k] and contiguous weights [experts, n, k] of one dtype")
+    if w2 is not None and (w2.shape != w1.shape or w2.dtype != w1.dtype or not w2.is_contiguous()):
+        raise KernelError("moe_gemm: the two weight stacks must agree")
+    if out.stride(1) != 1 or out.shape[1] != w1.shape[1]:
+        raise KernelError("moe_gemm output has the wrong shape or stride")
+    _check(library().mu_moe_gemm(_ptr(x), x.stride(0), _ptr(pair_of), int(top), _ptr(w1), _ptr(w2),
+                                 w1.stride(0), w1.stride(1), _ptr(tile_info), _ptr(n_tiles), int(max_tiles),
+                                 w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(x), _is_bf16(out),
+                                 _stream()), ("moe_gemm(n={}, k={})", w1.shape[1], w1.shape[2]))
+    return out
+
+
+def moe_combine(y: torch.Tensor, slot_of: torch.Tensor, weight_of: torch.Tensor, top: int, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over the token's choices, in their order, of weight * y[slot]; float32."""
+    _need_cuda(y, slot_of, weight_of, out)
+    if y.dtype != torch.float32 or out.dtype != torch.float32 or y.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("moe_combine works on float32 rows with unit inner stride")
+    _check(library().mu_moe_combine(_ptr(y), y.stride(0), _ptr(slot_of), _ptr(weight_of), out.shape[0], int(top),
+                                    out.shape[1], _ptr(out), out.stride(0), _stream()), "moe_combine")
     return out
 
 

@@ -47,9 +47,10 @@ class Assembly:
     layers: List[Layer]
     final_norm: object
     head: object
+    embedding_norm: object = None
 
     def parts(self):
-        out = [self.embedding, self.position]
+        out = [self.embedding, self.position] + ([self.embedding_norm] if self.embedding_norm is not None else [])
         for layer in self.layers:
             out.extend(layer.parts())
         out.extend([self.final_norm, self.head])
@@ -64,6 +65,7 @@ def assemble(plan: ModelPlan) -> Assembly:
         layers=[build_layer(spec) for spec in plan.layers],
         final_norm=build_part("norm", plan.final_norm),
         head=build_part("head", plan.head),
+        embedding_norm=build_part("norm", plan.embedding_norm) if plan.embedding_norm is not None else None,
     )
 
 

@@ -119,6 +119,8 @@ class DecoderModel:
     def forward(self, ctx, cache: SequenceCache) -> Optional[torch.Tensor]:
         a = self.assembly
         x = a.embedding.forward(ctx, a.position.embedding_table())
+        if a.embedding_norm is not None:
+            x = a.embedding_norm.forward_float(x, out=x)
         ctx.note("embed", x)
         for i, entry in enumerate(self.plan.schedule):
             layer = a.layers[entry.layer]

@@ -19,6 +19,7 @@ from .linear import Linear
 
 class CausalSelfAttention(Mixer):
     takes_lazy_norm = True
+    can_overwrite = True
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
@@ -54,7 +55,7 @@ class CausalSelfAttention(Mixer):
         self.qkv = Linear(tensors[self.tensor_name("qkv_weight")], self.bias_tensor(tensors, "qkv_bias"), runtime)
         self.out = Linear(tensors[self.tensor_name("out_weight")], self.bias_tensor(tensors, "out_bias"), runtime)
 
-    def forward(self, h, residual, ctx, cache, owns_cache: bool) -> None:
+    def forward(self, h, residual, ctx, cache, owns_cache: bool, accumulate: bool = True) -> None:
         qkv, q, k, v = ctx.buffer("attention.qkv", (ctx.n_tokens, self.q_width + 2 * self.kv_width),
                                   self.runtime.dtype, columns=(self.q_width, self.kv_width, self.kv_width))
         self.qkv(h, out=qkv)
@@ -63,7 +64,7 @@ class CausalSelfAttention(Mixer):
         attn = ctx.buffer("attention.out", (ctx.n_tokens, self.q_width), qkv.dtype)
         self.attend(q, k if owns_cache else None, v if owns_cache else None, attn, ctx, cache)
         ctx.note("attn", attn)
-        self.out(attn, residual=residual, out=residual)
+        self.out(attn, residual=residual if accumulate else None, out=residual)
 
     def attend(self, q, k_new, v_new, attn, ctx, cache) -> None:
         """Appends the step's keys and values (if given) to the cache pages and

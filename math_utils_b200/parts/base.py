@@ -34,7 +34,8 @@ class TensorSpec:
 
     ``shape`` is the shape on disk.  ``role`` is ``"matrix"`` (a GEMM operand,
     kept in the compute dtype), ``"table"`` (rows gathered by an index, kept in
-    the compute dtype), ``"vector"`` (bias or norm parameter, kept in 32-bit)
+    the compute dtype), ``"vector"`` (bias or norm parameter, kept in 32-bit),
+    ``"matrix32"`` (a small matrix whose product is always 32-bit: a router)
     or ``"int_table"`` (kept as int32).  ``transpose`` asks the loader for the
     transposed matrix (files that store ``[in, out]``; the kernels want
     ``[out, in]``, as the reference arranges at load:
@@ -56,6 +57,14 @@ class KVCacheSpec:
     keeps all of them; ``window`` w keeps what the last w positions need."""
     n_kv_heads: int
     head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class RowCacheSpec:
+    """A mixer that keeps ONE row of ``width`` values per earlier position, whatever its number of heads (a
+    compressed latent that every head reads); paged and windowed like keys and values."""
+    width: int
     window: int = 0
 
 
@@ -131,12 +140,18 @@ class Mixer(Part):
     """
 
     takes_lazy_norm = False          # see FeedForward
+    can_overwrite = False
 
     def cache_spec(self):
         return None
 
     def forward(self, h, residual, ctx, cache, owns_cache: bool) -> None:
         raise NotImplementedError
+
+
+# Mixers and feed-forwards that set ``can_overwrite`` take ``accumulate=False`` as a last argument of
+# ``forward`` and then WRITE their result to ``residual`` (a float32 buffer of the arrangement's) instead of
+# adding to it: for arrangements that norm a sublayer's output before it joins the residual stream.
 
 
 class FeedForward(Part):
@@ -146,6 +161,7 @@ class FeedForward(Part):
     passes it to its first ``Linear``, which folds the norm into the product
     where it can."""
     takes_lazy_norm = False
+    can_overwrite = False
 
     def forward(self, h, residual, ctx) -> None:
         raise NotImplementedError
@@ -162,6 +178,16 @@ class Norm(Part):
         """The norm as a ``NormedInput`` for a consumer that may fold it into
         its product; a norm that cannot be folded returns the computed tensor."""
         return self.forward(x, rows)
+
+    def forward_float(self, x, out=None):
+        """The normed rows as float32 (``out`` may be ``x``): a norm that sits ON the residual stream, for
+        instance right after the embedding."""
+        y = self.forward(x).float()
+        return y if out is None else out.copy_(y)
+
+    def add_into(self, y, residual) -> None:
+        """residual += norm(y), both float32: a norm on a sublayer's OUTPUT."""
+        residual += self.forward(y).float()
 
 
 class PositionEncoding(Part):

@@ -10,6 +10,11 @@ kernels take, goes to the library as ONE call that issues the layer's eight
 launches (``ops.prompt_layer``): the same kernels through the same entry
 points, without the host spending longer on the calls than the device on the
 kernels.  Every other layer, step and precision goes part by part.
+
+``sandwich_norm``: x += norm1b(mixer(norm1(x))); x += norm2b(feed_forward(norm2(x))), the two
+output norms given as the layer's extra parts ``norm1b`` and ``norm2b``.  A sublayer writes its
+result to a float32 buffer, and the output norm adds its normed rows into the residual stream.  A
+layer without a feed-forward (kind ``none``) stops after the mixer.
 """
 from __future__ import annotations
 
@@ -17,7 +22,7 @@ import torch
 
 from .attention import CausalSelfAttention
 from .base import Arrangement, PositionEncoding, register_part
-from .feedforward import DenseFeedForward
+from .feedforward import DenseFeedForward, NoFeedForward
 from .norm import LayerNorm
 
 
@@ -101,4 +106,29 @@ class PreNormBlock(Arrangement):
         return a
 
 
+class SandwichNormBlock(Arrangement):
+    def forward(self, x, layer, ctx, cache, owns_cache: bool) -> None:
+        y = ctx.buffer("sublayer.out", tuple(x.shape), torch.float32)
+        h = layer.norm1.forward(x)
+        ctx.note("ln1", h)
+        self._sublayer(layer.mixer, y, h, y, ctx, cache, owns_cache)
+        layer.extra["norm1b"].add_into(y, x)
+        ctx.note("res1", x)
+        if not isinstance(layer.feed_forward, NoFeedForward):
+            h = layer.norm2.forward(x)
+            ctx.note("ln2", h)
+            self._sublayer(layer.feed_forward, y, h, y, ctx)
+            layer.extra["norm2b"].add_into(y, x)
+        ctx.note("res2", x)
+
+    @staticmethod
+    def _sublayer(part, y, *args):
+        if part.can_overwrite:
+            part.forward(*args, accumulate=False)
+        else:                                  # a part that can only add: into zeros
+            y.zero_()
+            part.forward(*args)
+
+
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)
+register_part("arrangement", "sandwich_norm", SandwichNormBlock, replace=True)

@@ -1,6 +1,8 @@
-"""Token embedding: a row of the table per token, plus the position table's
-row when the position encoding has one; the result is the float32 residual
-stream (include/ai/LocalModel.hpp:3686-3697)."""
+"""Token embedding: a row of the table per token (times the parameter
+``scale``, 1 if absent), plus the position table's row when the position
+encoding has one; the result is the float32 residual stream
+(include/ai/LocalModel.hpp:3686-3697).  Heads: ``tied_head`` (the token table
+itself) and ``linear_head`` (a matrix of its own, no bias)."""
 from __future__ import annotations
 
 from ..config.base import PartSpec
@@ -12,6 +14,7 @@ class TokenEmbedding(Embedding):
         super().__init__(spec)
         self.vocab_size = int(self.param("vocab_size"))
         self.hidden_size = int(self.param("hidden_size"))
+        self.scale = float(self.param("scale", 1.0))
 
     def tensor_specs(self):
         return (TensorSpec(self.tensor_name("weight"), (self.vocab_size, self.hidden_size), role="table"),)
@@ -24,7 +27,7 @@ class TokenEmbedding(Embedding):
         return self.weight
 
     def forward(self, ctx, position_table):
-        return self.runtime.ops.embed(ctx.token_ids, ctx.tok_pos, self.weight, position_table)
+        return self.runtime.ops.embed(ctx.token_ids, ctx.tok_pos, self.weight, position_table, scale=self.scale)
 
 
 class TiedHead(Head):
@@ -51,5 +54,28 @@ class TiedHead(Head):
         return self.linear(h, out_dtype=torch.float32)
 
 
+class LinearHead(Head):
+    """Logits = h @ W^T with an output matrix ``weight`` [vocab, hidden] of its own, no bias."""
+    takes_lazy_norm = True
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.vocab_size = int(self.param("vocab_size"))
+        self.hidden_size = int(self.param("hidden_size"))
+
+    def tensor_specs(self):
+        return (TensorSpec(self.tensor_name("weight"), (self.vocab_size, self.hidden_size), role="matrix"),)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        from .linear import Linear
+        self.linear = Linear(tensors[self.tensor_name("weight")], None, runtime)
+
+    def forward(self, h):
+        import torch
+        return self.linear(h, out_dtype=torch.float32)
+
+
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)
+register_part("head", "linear_head", LinearHead, replace=True)
 register_part("head", "tied_head", TiedHead, replace=True)

@@ -14,6 +14,7 @@ ACTIVATIONS = ("gelu_new", "gelu")
 
 class DenseFeedForward(FeedForward):
     takes_lazy_norm = True
+    can_overwrite = True
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
@@ -38,13 +39,23 @@ class DenseFeedForward(FeedForward):
         self.up = Linear(tensors[self.tensor_name("up_weight")], self.bias_tensor(tensors, "up_bias"), runtime)
         self.down = Linear(tensors[self.tensor_name("down_weight")], self.bias_tensor(tensors, "down_bias"), runtime)
 
-    def forward(self, h, residual, ctx) -> None:
+    def forward(self, h, residual, ctx, accumulate: bool = True) -> None:
         hidden = None if ctx is None else ctx.buffer("feed_forward.hidden", (ctx.n_tokens, self.inner_size),
                                                      self.runtime.dtype)
         u = self.up(h, act=self.activation, out=hidden)
         if ctx is not None:
             ctx.note("act", u)
-        self.down(u, residual=residual, out=residual)
+        self.down(u, residual=residual if accumulate else None, out=residual)
+
+
+class NoFeedForward(FeedForward):
+    """A layer that ends after its mixer."""
+    can_overwrite = True
+
+    def forward(self, h, residual, ctx, accumulate: bool = True) -> None:
+        if not accumulate:
+            residual.zero_()
 
 
 register_part("feed_forward", "dense_ffn", DenseFeedForward, replace=True)
+register_part("feed_forward", "none", NoFeedForward, replace=True)

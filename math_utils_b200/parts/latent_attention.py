@@ -1,0 +1,121 @@
+"""Attention through a shared low-rank latent.
+
+Parameters: ``hidden_size, n_heads, dim`` (unrotated query/key entries per head), ``rot_dim`` (rotated
+entries per head), ``vdim`` (value entries per head), ``kv_rank`` (latent size), ``softmax_scale``,
+``eps`` (of the latent's RMS norm), ``rot`` = {base, dims, scaling?} and ``own_kv`` (false for a layer
+that reads the latent cache of an earlier layer and has no down-projection of its own).
+
+Per token the layer keeps ONE row for all heads: the RMS-normed latent c (kv_rank values) and one
+rotated key part (rot_dim values).  With k_h = U_h c and v_h = V_h c the score of head h is
+    (q_h^n . U_h c + q_h^r . k^r) * scale = ((U_h^T q_h^n) . c + q_h^r . k^r) * scale
+and the head's output V_h (sum_j p_j c_j), so the attention itself runs in latent space over the
+cached rows, the same rows for every head, and the two up-projections become products per head before
+and after it: keys and values are never expanded.  An output gate sigmoid(G h) multiplies the
+concatenated heads before the output projection.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.base import ConfigError, PartSpec
+from .base import Mixer, RowCacheSpec, TensorSpec, register_part
+from .linear import Linear
+from .position import rotary_frequencies
+
+
+class LatentAttention(Mixer):
+    can_overwrite = True
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = self.param
+        self.hidden_size, self.n_heads = int(p("hidden_size")), int(p("n_heads"))
+        self.dim, self.rot_dim, self.vdim, self.kv_rank = int(p("dim")), int(p("rot_dim")), int(p("vdim")), int(p("kv_rank"))
+        self.scale, self.eps = float(p("softmax_scale")), float(p("eps"))
+        self.own_kv = bool(p("own_kv", True))
+        self.window = int(p("window", 0))
+        rot = p("rot")
+        self.rot_dims = int(rot["dims"])
+        if self.rot_dims > self.rot_dim or self.rot_dims % 2:
+            raise ConfigError(f"latent_attention: {self.rot_dims} rotated entries do not fit the rotated part of {self.rot_dim}")
+        self.freqs, self.magnitude = rotary_frequencies(self.rot_dims, float(rot["base"]), rot.get("scaling"))
+        self.q_head = self.dim + self.rot_dim
+        self.row = self.kv_rank + self.rot_dim
+
+    def tensor_specs(self):
+        H, D, r = self.n_heads, self.hidden_size, self.kv_rank
+        name = self.tensor_name
+        specs = [TensorSpec(name("q"), (H * self.q_head, D))]
+        if self.own_kv:
+            specs += [TensorSpec(name("dkv"), (self.row, D)),
+                      TensorSpec(name("dkv_norm"), (r,), role="vector", init="norm_weight")]
+        specs += [TensorSpec(name("uk"), (H * self.dim, r)), TensorSpec(name("uv"), (H * self.vdim, r)),
+                  TensorSpec(name("gate"), (H * self.vdim, D)),
+                  TensorSpec(name("out"), (D, H * self.vdim), init="residual_projection")]
+        return specs
+
+    def cache_spec(self):
+        return RowCacheSpec(self.row, self.window)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        t = lambda role: tensors[self.tensor_name(role)]
+        H = self.n_heads
+        # one product for everything that reads the layer's input: queries | gate | down-projection
+        parts = [t("q"), t("gate")] + ([t("dkv")] if self.own_kv else [])
+        self.widths = tuple(w.shape[0] for w in parts)
+        self.proj = Linear(torch.cat(parts, dim=0).contiguous(), None, runtime)
+        self.norm_weight = t("dkv_norm") if self.own_kv else None
+        # U_h^T as [kv_rank, dim] per head ([out, in] for the product that carries a query into latent space)
+        uk = t("uk").reshape(H, self.dim, self.kv_rank)
+        self.q_up = [Linear(uk[h].t().contiguous(), None, runtime) for h in range(H)]
+        uv = t("uv").reshape(H, self.vdim, self.kv_rank)
+        self.v_up = [Linear(uv[h].contiguous(), None, runtime) for h in range(H)]
+        self.out = Linear(t("out"), None, runtime)
+        self.freq_table = torch.tensor(self.freqs, dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+    def forward(self, h, residual, ctx, cache, owns_cache: bool, accumulate: bool = True) -> None:
+        ops, dt = self.runtime.ops, self.runtime.dtype
+        T, H, r = ctx.n_tokens, self.n_heads, self.kv_rank
+        views = ctx.buffer("latent.proj", (T, sum(self.widths)), dt, columns=self.widths)
+        proj, q, gate = views[0], views[1], views[2]
+        self.proj(h, out=proj)
+        ctx.note("proj", proj)
+        table = ctx.block_tables[cache.group]
+        if owns_cache:
+            if not self.own_kv:
+                raise ConfigError("a latent-attention layer without a down-projection cannot own a cache")
+            ops.latent_append(views[3], self.norm_weight, self.eps, self.freq_table, self.magnitude, self.rot_dims,
+                              r, self.rot_dim, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens, cache.pages)
+        # queries in latent space, float32: [T, H, kv_rank | rot_dim]
+        qa = ctx.buffer("latent.q", (T, H * self.row), torch.float32)
+        for i in range(H):
+            self.q_up[i](q[:, i * self.q_head: i * self.q_head + self.dim], out=qa[:, i * self.row: i * self.row + r])
+        ops.rotary(q[:, self.dim:], qa[:, r:], ctx.tok_pos, self.freq_table, self.magnitude, H, self.rot_dims,
+                   self.rot_dim, self.q_head, self.row)
+        ctx.note("q_latent", qa)
+        mixed = ctx.buffer("latent.mixed", (T, H * r), dt)
+        n_splits, part_o, part_ml = self.splits(ctx)
+        ops.latent_attention(qa, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq, H, r, self.scale,
+                             mixed, n_splits, part_o, part_ml)
+        heads = ctx.buffer("latent.heads", (T, H * self.vdim), dt)
+        for i in range(H):
+            self.v_up[i](mixed[:, i * r: (i + 1) * r], out=heads[:, i * self.vdim: (i + 1) * self.vdim])
+        ops.sigmoid_gate(heads, gate)
+        ctx.note("attn", heads)
+        self.out(heads, residual=residual if accumulate else None, out=residual)
+
+    def splits(self, ctx):
+        """Single-token steps cut each head's rows into parts so that the blocks fill the GPU; a part is never
+        shorter than 128 rows of the longest sequence the step may hold."""
+        if not ctx.is_decode:
+            return 1, None, None
+        items = ctx.n_tokens * self.n_heads
+        by_fill = -(-(4 * self.runtime.ops.sm_count(self.runtime.device)) // items)
+        n = max(1, min(by_fill, -(-ctx.max_kv_len // 128), 32))
+        if n == 1:
+            return 1, None, None
+        return n, ctx.scratch("latent_part_o", items * n * self.kv_rank), ctx.scratch("latent_part_ml", items * n * 2)
+
+
+register_part("mixer", "latent_attention", LatentAttention, replace=True)

@@ -129,7 +129,7 @@ def arrange(t: torch.Tensor, spec: TensorSpec, compute_dtype: torch.dtype, devic
     if not t.dtype.is_floating_point:
         raise WeightError(spec.name, other=[f"tensor '{spec.name}' should hold floats, holds {t.dtype}"])
     t = t.to(device)
-    if spec.role == "vector":
+    if spec.role in ("vector", "matrix32"):
         return t.to(torch.float32).contiguous()
     if spec.role in ("matrix", "table"):
         t = t.to(compute_dtype)
