@@ -317,7 +317,7 @@ def rotary(x: torch.Tensor, out: torch.Tensor, tok_pos: torch.Tensor, freqs: tor
     are copied.  ``x`` and ``out`` are views whose first element is head 0's first entry; they may be the same."""
     _need_cuda(x, out, tok_pos, freqs)
     _i32(tok_pos, "tok_pos")
-    if freqs.dtype != torch.float32 or freqs.numel() != dims // 2 or dims % 2:
+    if freqs.dtype != torch.float32 or freqs.numel() < dims // 2 or dims % 2:
         raise KernelError("rotary wants dims / 2 float32 frequencies")
     _check(library().mu_rotary(_ptr(x), x.stride(0), int(x_head_stride), _is_bf16(x), _ptr(out), out.stride(0),
                                int(out_head_stride), _is_bf16(out), _ptr(tok_pos), _ptr(freqs), float(magnitude),

@@ -72,7 +72,8 @@ class LatentAttention(Mixer):
         uv = t("uv").reshape(H, self.vdim, self.kv_rank)
         self.v_up = [Linear(uv[h].contiguous(), None, runtime) for h in range(H)]
         self.out = Linear(t("out"), None, runtime)
-        self.freq_table = torch.tensor(self.freqs, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        # (one entry at least, so that the kernels always get a table)
+        self.freq_table = torch.tensor(self.freqs or [0.0], dtype=torch.float64).to(torch.float32).to(runtime.device)
 
     def forward(self, h, residual, ctx, cache, owns_cache: bool, accumulate: bool = True) -> None:
         ops, dt = self.runtime.ops, self.runtime.dtype
@@ -91,8 +92,9 @@ class LatentAttention(Mixer):
         qa = ctx.buffer("latent.q", (T, H * self.row), torch.float32)
         for i in range(H):
             self.q_up[i](q[:, i * self.q_head: i * self.q_head + self.dim], out=qa[:, i * self.row: i * self.row + r])
-        ops.rotary(q[:, self.dim:], qa[:, r:], ctx.tok_pos, self.freq_table, self.magnitude, H, self.rot_dims,
-                   self.rot_dim, self.q_head, self.row)
+        if self.rot_dim:
+            ops.rotary(q[:, self.dim:], qa[:, r:], ctx.tok_pos, self.freq_table, self.magnitude, H, self.rot_dims,
+                       self.rot_dim, self.q_head, self.row)
         ctx.note("q_latent", qa)
         mixed = ctx.buffer("latent.mixed", (T, H * r), dt)
         n_splits, part_o, part_ml = self.splits(ctx)

@@ -57,7 +57,7 @@ def random_tensors(config, plan, seed: int, store_dtype: torch.dtype) -> Dict[st
         values = values * np.float32(std) + np.float32(mean)
         if spec.role == "int_table":
             raise ValueError(f"tensor '{spec.name}': no random rule for integer tables")
-        out[spec.name] = torch.from_numpy(values).to(store_dtype)
+        out[spec.name] = torch.from_numpy(np.asarray(values, dtype=np.float32)).to(store_dtype)
     return out
 
 
