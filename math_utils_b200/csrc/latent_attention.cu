@@ -293,3 +293,17 @@ MU_EXPORT int mu_latent_attention(const float* q, const void* rows, const int* b
     return mu::launch_pdl(mu::latent_merge_kernel<float>, grid, block, 0, s, 1, (const float*)part_o,
                           (const float*)part_ml, n_heads, kv_rank, n_splits, (float*)out, ldo);
 }
+
+// Merges the partial results of n_splits parts of every (token, head) into out (bfloat16 or float32).
+MU_EXPORT int mu_latent_merge(const float* part_o, const float* part_ml, int n_tokens, int n_heads, int kv_rank,
+                              int n_splits, void* out, long long ldo, int is_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!part_o || !part_ml || !out || n_heads <= 0 || kv_rank <= 0 || n_splits < 1) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_tokens * n_heads), block(128);
+    if (is_bf16)
+        return mu::launch_pdl(mu::latent_merge_kernel<__nv_bfloat16>, grid, block, 0, s, 1, part_o, part_ml, n_heads,
+                              kv_rank, n_splits, (__nv_bfloat16*)out, ldo);
+    return mu::launch_pdl(mu::latent_merge_kernel<float>, grid, block, 0, s, 1, part_o, part_ml, n_heads, kv_rank,
+                          n_splits, (float*)out, ldo);
+}

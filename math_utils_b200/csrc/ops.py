@@ -43,7 +43,9 @@ def _switch(name: str) -> bool:
 #   MU_B200_PDL=0         plain stream order between kernels (no programmatic dependent launch)
 #   MU_B200_ATT_TC=0      single-token attention on CUDA cores instead of mma.sync
 #   MU_B200_PREFILL_TC=0  prompt attention on mma.sync instead of tcgen05
+#   MU_B200_LATENT_TC=0   latent attention and the experts' products on CUDA cores instead of mma.sync
 PDL, ATT_TC, PREFILL_TC = _switch("MU_B200_PDL"), _switch("MU_B200_ATT_TC"), _switch("MU_B200_PREFILL_TC")
+LATENT_TC = _switch("MU_B200_LATENT_TC")
 
 _c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
 
@@ -90,6 +92,10 @@ _SIGNATURES = {
                          _c_int, _c_p, _c_int, _c_p],
     "mu_latent_attention": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int,
                             _c_p, _c_ll, _c_p, _c_p, _c_int, _c_p],
+    "mu_latent_merge": [_c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p],
+    "mu_latent_attention_mma_fits": [_c_int, _c_int, _c_int],
+    "mu_latent_attention_mma": [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f,
+                                _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p],
     "mu_moe_route": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p,
                      _c_p],
     "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p],
@@ -345,10 +351,18 @@ def latent_append(dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, freq
 
 def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Tensor, page_tokens: int, tok_pos, tok_seq,
                      n_heads: int, kv_rank: int, scale: float, out: torch.Tensor, n_splits: int = 1,
-                     part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                     tiles: Optional[torch.Tensor] = None, single_tokens: bool = False,
+                     tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """Attention of float32 queries [T, n_heads, width] over the latent rows 0..position of each token's sequence;
-    ``out`` [T, n_heads * kv_rank] receives the weighted sums of the rows' first ``kv_rank`` values."""
-    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, part_o, part_ml)
+    ``out`` [T, n_heads * kv_rank] receives the weighted sums of the rows' first ``kv_rank`` values.
+
+    bfloat16 caches at the sizes ``mu_latent_attention_mma`` takes go to the tensor cores when the step says how its
+    tokens group: ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of runs of tokens of one sequence) or
+    ``single_tokens`` (every token is the one token of its sequence); ``tensor_cores`` false keeps the CUDA-core
+    kernel.  ``n_splits`` > 1 (single-token steps) cuts each sequence's rows into parts that are merged afterwards."""
+    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, part_o, part_ml, tiles)
+    _i32(tiles, "tiles")
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
     width = rows.shape[2]
@@ -362,6 +376,21 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
         if (part_o is None or part_ml is None or part_o.numel() < need * kv_rank or part_ml.numel() < need * 2
                 or part_o.dtype != torch.float32 or part_ml.dtype != torch.float32):
             raise KernelError("split attention needs float32 scratch for its partial results")
+    if tensor_cores is None:
+        tensor_cores = LATENT_TC
+    if (tensor_cores and rows.dtype == torch.bfloat16 and (tiles is not None or single_tokens)
+            and out.stride(0) % 2 == 0 and library().mu_latent_attention_mma_fits(int(kv_rank), int(width), int(page_tokens))):
+        if tiles is not None:
+            n_splits = 1
+        what = ("latent_attention_mma(heads={}, kv_rank={}, width={})", n_heads, kv_rank, width)
+        _check(library().mu_latent_attention_mma(
+            _ptr(q), _ptr(rows), _ptr(block_table), block_table.shape[1], _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles),
+            tiles.shape[0] if tiles is not None else 0, n_tokens, int(n_heads), int(kv_rank), int(width), float(scale),
+            int(n_splits), _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _stream()), what)
+        if n_splits > 1:
+            _check(library().mu_latent_merge(_ptr(part_o), _ptr(part_ml), n_tokens, int(n_heads), int(kv_rank),
+                                             int(n_splits), _ptr(out), out.stride(0), 1, _stream()), what)
+        return out
     _check(library().mu_latent_attention(_ptr(q), _ptr(rows), _ptr(block_table), block_table.shape[1], int(page_tokens),
                                          _ptr(tok_pos), _ptr(tok_seq), n_tokens, int(n_heads), int(kv_rank), int(width),
                                          float(scale), int(n_splits), _ptr(out), out.stride(0), _ptr(part_o),

@@ -99,7 +99,7 @@ class LatentAttention(Mixer):
         mixed = ctx.buffer("latent.mixed", (T, H * r), dt)
         n_splits, part_o, part_ml = self.splits(ctx)
         ops.latent_attention(qa, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq, H, r, self.scale,
-                             mixed, n_splits, part_o, part_ml)
+                             mixed, n_splits, part_o, part_ml, tiles=ctx.q_tiles, single_tokens=ctx.is_decode)
         heads = ctx.buffer("latent.heads", (T, H * self.vdim), dt)
         for i in range(H):
             self.v_up[i](mixed[:, i * r: (i + 1) * r], out=heads[:, i * self.vdim: (i + 1) * self.vdim])
@@ -108,12 +108,14 @@ class LatentAttention(Mixer):
         self.out(heads, residual=residual if accumulate else None, out=residual)
 
     def splits(self, ctx):
-        """Single-token steps cut each head's rows into parts so that the blocks fill the GPU; a part is never
+        """Single-token steps cut each sequence's rows into parts so that the blocks fill the GPU; a part is never
         shorter than 128 rows of the longest sequence the step may hold."""
         if not ctx.is_decode:
             return 1, None, None
         items = ctx.n_tokens * self.n_heads
-        by_fill = -(-(4 * self.runtime.ops.sm_count(self.runtime.device)) // items)
+        tc = self.runtime.dtype == torch.bfloat16 and self.runtime.ops.LATENT_TC
+        blocks = ctx.n_tokens * -(-self.n_heads // 32) if tc else items      # the tensor-core kernel: 32 heads a block
+        by_fill = -(-((2 if tc else 4) * self.runtime.ops.sm_count(self.runtime.device)) // blocks)
         n = max(1, min(by_fill, -(-ctx.max_kv_len // 128), 32))
         if n == 1:
             return 1, None, None

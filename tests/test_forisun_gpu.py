@@ -329,11 +329,48 @@ def test_latent_attention_kernel(dtype, heads, kv_rank, rot_dim, n_splits):
     items = len(picks) * heads
     part_o = torch.zeros(items * n_splits * kv_rank, device="cuda")
     part_ml = torch.zeros(items * n_splits * 2, device="cuda")
-    ops.latent_attention(dev(q.reshape(len(picks), -1)), dev(pages, dtype), dev(table, torch.int32), 64,
-                         dev(np.array([p for _, p in picks]), torch.int32), dev(np.array([s for s, _ in picks]), torch.int32),
-                         heads, kv_rank, scale, out, n_splits, part_o, part_ml)
+    args = (dev(q.reshape(len(picks), -1)), dev(pages, dtype), dev(table, torch.int32), 64,
+            dev(np.array([p for _, p in picks]), torch.int32), dev(np.array([s for s, _ in picks]), torch.int32),
+            heads, kv_rank, scale, out, n_splits, part_o, part_ml)
+    ops.latent_attention(*args, tensor_cores=False)
     got = out.float().cpu().numpy().reshape(len(picks), heads, kv_rank)
     assert np.abs(got - want).max() < (2e-5 if dtype == torch.float32 else 2e-2)
+    if dtype == torch.bfloat16 and kv_rank % 64 == 0:
+        # the same on tensor cores: every query as its sequence's single token (queries and weights rounded to bfloat16)
+        out.zero_()
+        ops.latent_attention(*args, single_tokens=True, tensor_cores=True)
+        got = out.float().cpu().numpy().reshape(len(picks), heads, kv_rank)
+        assert np.abs(got - want).max() < 4e-2
+        assert np.abs(got[5, 0] - seqs[5][far, :kv_rank]).max() < 0.5 * abs(seqs[5][far, :kv_rank]).max()
+
+
+@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(3, 64, 16), (6, 128, 32), (16, 256, 32), (40, 64, 0), (2, 512, 64)])
+def test_latent_attention_on_tensor_cores_prompt_tiles(heads, kv_rank, rot_dim):
+    """Whole prompts of several sequences in one step: tiles of up to 64 tokens, every token its own causal edge."""
+    ops, rng = _ops(), np.random.default_rng(8)
+    lens = [130, 1, 64, 65, 7]
+    seqs, pages, table = _latent_case(rng, lens, heads, kv_rank, rot_dim)
+    width, scale = kv_rank + rot_dim, 0.21
+    pages = dev(pages, torch.bfloat16).float().cpu().numpy().astype(np.float64)
+    seqs = [np.concatenate([pages[table[s, i]] for i in range(-(-n // 64))])[:n] for s, n in enumerate(lens)]
+    T = sum(lens)
+    q = dev(rng.normal(0, 1, (T, heads, width)) / math.sqrt(width) * 4, torch.bfloat16).float().cpu().numpy().astype(np.float64)
+    tok_seq = np.repeat(np.arange(len(lens)), lens)
+    tok_pos = np.concatenate([np.arange(n) for n in lens])
+    tiles, at = [], 0
+    for n in lens:
+        tiles += [(at + o, min(64, n - o)) for o in range(0, n, 64)]
+        at += n
+    tiles.sort(key=lambda t: -tok_pos[t[0] + t[1] - 1])
+    want = np.stack([[_plain_latent(q[t, h], seqs[tok_seq[t]][:tok_pos[t] + 1], kv_rank, scale) for h in range(heads)]
+                     for t in range(T)])
+    out = torch.zeros((T, heads * kv_rank), device="cuda", dtype=torch.bfloat16)
+    ops.latent_attention(dev(q.reshape(T, -1)), dev(pages, torch.bfloat16), dev(table, torch.int32), 64,
+                         dev(tok_pos, torch.int32), dev(tok_seq, torch.int32), heads, kv_rank, scale, out,
+                         tiles=dev(np.array(tiles), torch.int32), tensor_cores=True)
+    got = out.float().cpu().numpy().reshape(T, heads, kv_rank)
+    err = np.abs(got - want).max(axis=(1, 2))
+    assert err.max() < 4e-2, f"first wrong token {int(np.argmax(err > 4e-2))} (sequence {tok_seq[np.argmax(err > 4e-2)]}, position {tok_pos[np.argmax(err > 4e-2)]})"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
