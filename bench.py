@@ -4,6 +4,7 @@
     python bench.py --config medium|xl          # BASELINE.json's fourth and fifth workloads
     python bench.py --only decode|prefill [--layers N] [--batch B]     # a small case for a profiler
     python bench.py --only marginal [--batch B]    # each kernel class's share of the recorded decode step
+    python bench.py --family forisun [--size s|m] [--batch B] [--steps K]   # Forisun beside GPT-2 at equal size
 
 A "step" is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (BASELINE.json's third configuration) with seeded random
@@ -450,6 +451,85 @@ def run_part(args):
     return 0
 
 
+FORISUN_SIZES = {
+    # width, heads, dim, rot_dim, vdim, kv_rank, experts, top, expert ff, dense ff, layers
+    "s": (1024, 8, 64, 32, 64, 256, 16, 4, 512, 4096, 4),
+    "m": (2048, 16, 128, 64, 128, 512, 64, 6, 1408, 8192, 4),
+}
+FAMILY_VOCAB = 32768
+
+
+def forisun_config(size):
+    """A Forisun configuration with layer sizes of a real model's order (random weights): one dense layer, then
+    layers of routed experts; and the GPT-2 configuration of equal width, layer count, vocabulary and feed-forward
+    work per token (a gated expert has three matrices where GPT-2's feed-forward has two), head size 64."""
+    D, H, dn, dr, dv, r, E, top, ff, dense, L = FORISUN_SIZES[size]
+    mixer = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": (dn + dr) ** -0.5,
+             "rot": {"base": 10000.0, "dims": dr, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top, "scale": 2.5}}
+    layers = [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": dense} if i == 0 else moe}
+              for i in range(L)]
+    ours = {"architecture": "Forisun", "vocab": FAMILY_VOCAB, "width": D, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "layers": layers}
+    twin = {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "n_layer": L, "n_embd": D, "n_head": D // 64,
+            "n_inner": top * ff * 3 // 2, "vocab_size": FAMILY_VOCAB, "n_positions": CONTEXT,
+            "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new"}
+    return ours, twin
+
+
+def stage_times(model, prompts, single_steps=8):
+    """Device milliseconds per stage of one eager prompt step and of eager single-token steps (their mean)."""
+    import torch
+    from math_utils_b200 import StepEntry
+    from math_utils_b200.engine.stage_timer import StageTimer
+    cache = model.new_cache(max_tokens=len(prompts) * CONTEXT, n_slots=len(prompts))
+    out = {}
+    for warm in (True, False):
+        slots = [cache.acquire() for _ in prompts]
+        timer = StageTimer()
+        timer.begin(True)
+        model.step(cache, [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)], trace=timer)
+        for _ in range(single_steps):
+            timer.begin(False)
+            model.step(cache, [StepEntry(s, [1], [0]) for s in slots], trace=timer)
+        if not warm:
+            out = {k: [round(a * 1e3, 4), round(b * 1e3 / single_steps, 4)] for k, (a, b) in timer.totals().items() if a or b}
+        for s in slots:
+            cache.release(s)
+    return out
+
+
+def run_family(args):
+    """``--family forisun``: prompt and single-token throughput of Forisun at sizes of a real model's order beside
+    GPT-2 at equal size, the same workload shape as the default run (2 x 1,024-token prompts; a batch from
+    512-token prompts towards 1,024).  Prints one JSON line; the default run and its line are not touched."""
+    import numpy as np
+    from math_utils_b200.sampling import SamplingParams
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    record = {"family": "forisun", "size": args.size, "batch": args.batch, "steps": args.steps, "dtype": "bfloat16",
+              "data": "synthetic: random weights, random tokens", "peaks": pk, "models": {}}
+    for name, cfg in zip(("forisun", "gpt2_twin"), forisun_config(args.size)):
+        llm = load_random(cfg, temperature=0.0, context=CONTEXT)
+        model = llm.model
+        pre = [rng.integers(0, FAMILY_VOCAB, size=CONTEXT).tolist() for _ in range(PREFILL_SEQS)]
+        ms, host_ms = time_prefill(model, pre, repeats=5, warmup=3)
+        prompts = [rng.integers(0, FAMILY_VOCAB, size=args.prompt_len).tolist() for _ in range(args.batch)]
+        r = time_decode(model, prompts, args.steps, max(args.warmup, 3), SamplingParams(temperature=0.0), check_steps=0)
+        step_ms = r["seconds"] / args.steps * 1e3
+        record["models"][name] = {
+            "weight_bytes": model.weight_bytes,
+            "prefill": {"tokens": PREFILL_SEQS * CONTEXT, "ms": round(ms, 3), "host_ms": round(host_ms, 3),
+                        "tokens_per_s": round(PREFILL_SEQS * CONTEXT / ms * 1e3)},
+            "decode": {"ms_per_step": round(step_ms, 4), "tokens_per_s": round(args.batch / step_ms * 1e3),
+                       "ctx_first": r["ctx_first"], "ctx_last": r["ctx_last"], "launches_per_step": r["launches"] // args.steps},
+            "stages_ms": stage_times(model, [p[:CONTEXT // 2] for p in pre]),
+        }
+        del llm, model
+    print(json.dumps(record), flush=True)
+    return 0
+
+
 def run_marginal(args):
     """What each class of launches costs INSIDE the recorded, overlapped single-token step: the step is
     recorded again with that class left out (its outputs are then stale, which no timing cares about), and
@@ -613,6 +693,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="with --only decode: tokens per prompt")
     ap.add_argument("--reference-dir", default="", help="with --impl reference: a checkout other than baseline/_ref")
     ap.add_argument("--tokens", type=int, default=0, help="with --config: fewer tokens per request than fill the context")
+    ap.add_argument("--family", default="", choices=["", "forisun"],
+                    help="forisun: that design at sizes of a real model's order beside GPT-2 at equal size")
+    ap.add_argument("--size", default="s", choices=sorted(FORISUN_SIZES), help="with --family: which sizes")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this library has no multi-GPU path (asked for {args.gpus})",
@@ -620,6 +703,8 @@ def main():
         return 2
     if args.impl == "reference":
         return run_reference(args)
+    if args.family:
+        return run_family(args)
     if args.only == "marginal":
         return run_marginal(args)
     if args.config != "small":

@@ -5,7 +5,7 @@
 //
 // mu_moe_route    z = W_r h in float32; s = sigmoid(z) (or softmax over the experts); the `top` experts with
 //                 the largest s + correction are chosen (ties: the lower index); weight = s * scale
-//                 (optionally divided by the chosen experts' sum).  One warp per token.
+//                 (optionally divided by the chosen experts' sum).  One block per token.
 // mu_moe_group    counts the pairs of each expert, gives every pair a slot so that an expert's slots are
 //                 contiguous, and lists tiles of TM slots that never straddle two experts.
 // mu_moe_gemm     for every tile: out[slot, :] = act(W1[e] x[row]) (* W2[e] x[row]) on CUDA cores, one running
@@ -21,28 +21,36 @@ namespace mu {
 
 constexpr int MOE_TM = 32, MOE_TN = 64, MOE_TK = 32;
 
+constexpr int ROUTE_WARPS = 8;
+
+// One block per token: the token's row is staged in shared memory as float32, the warps share the experts (each
+// logit one warp's sum over the row, lanes striding along it), then the first warp scores and chooses.
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ router,
-                                 const float* __restrict__ correction, int n_tokens, int hidden, int n_experts, int top,
-                                 float scale, int softmax, int renormalize, int* __restrict__ expert_of,
-                                 float* __restrict__ weight_of) {
-    extern __shared__ float sm[];                      // per warp: scores [n_experts], choice [n_experts]
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ router,
+                 const float* __restrict__ correction, int n_tokens, int hidden, int n_experts, int top,
+                 float scale, int softmax, int renormalize, int* __restrict__ expert_of,
+                 float* __restrict__ weight_of) {
+    extern __shared__ float sm[];                      // row [hidden], scores [n_experts], choice [n_experts]
     pdl_trigger();
     pdl_wait();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    const int t = blockIdx.x * warps + warp;
-    if (t >= n_tokens) return;
-    float* score = sm + (size_t)warp * 2 * n_experts;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x;
+    float* hrow = sm;
+    float* score = sm + hidden;
     float* choice = score + n_experts;
     const T* row = h + (long long)t * ldh;
-    for (int e = 0; e < n_experts; ++e) {
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) hrow[d] = to_float(row[d]);
+    __syncthreads();
+    for (int e = warp; e < n_experts; e += ROUTE_WARPS) {
         const float* w = router + (long long)e * hidden;
         float z = 0.0f;
-        for (int d = lane; d < hidden; d += 32) z += to_float(row[d]) * w[d];
+        for (int d = lane; d < hidden; d += 32) z += hrow[d] * w[d];
         z = warp_sum(z);
         if (lane == 0) score[e] = z;
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     if (softmax) {
         float top_z = -INFINITY, sum = 0.0f;
         for (int e = lane; e < n_experts; e += 32) top_z = fmaxf(top_z, score[e]);
@@ -224,11 +232,10 @@ MU_EXPORT int mu_moe_route(const void* h, long long ldh, int h_bf16, const float
     if (n_tokens <= 0) return MU_OK;
     if (!h || !router || !expert_of || !weight_of || hidden <= 0 || n_experts <= 0 || top <= 0 || top > n_experts)
         return MU_ERR_BAD_ARGUMENT;
-    const int warps = 4;
-    const size_t smem = (size_t)warps * 2 * n_experts * sizeof(float);
+    const size_t smem = (size_t)(hidden + 2 * n_experts) * sizeof(float);
     if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid((n_tokens + warps - 1) / warps), block(warps * 32);
+    const dim3 grid(n_tokens), block(mu::ROUTE_WARPS * 32);
     if (h_bf16)
         return mu::launch_pdl(mu::moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, 1, (const __nv_bfloat16*)h, ldh,
                               router, correction, n_tokens, hidden, n_experts, top, scale, softmax, renormalize,

@@ -1,0 +1,179 @@
+// The experts' products on tensor cores (mma.sync m16n8k16, bfloat16, float32 accumulation).
+//
+// Same work list as the CUDA-core kernel of moe.cu: tiles of up to 32 slots of one expert (tile_info), rows of x
+// gathered through the slots' pairs or taken by slot.  A block computes 32 rows x 128 output columns: eight
+// warps of 32 x 16 each, operands staged in shared memory by cp.async in chunks of 64 along k (two stages) and
+// read as fragments with ldmatrix.  GATED: two weight stacks, out = silu(W1 x) * (W2 x).  Every output is one
+// running sum over k in order, whatever shares its tile.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace mu {
+
+constexpr int MM_ROWS = 32, MM_COLS = 128, MM_K = 64, MM_PITCH = MM_K + 8, MM_THREADS = 256;
+
+__device__ __forceinline__ void mm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mm_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// 16 bytes to shared memory, of which the first `bytes` come from global memory and the rest are zero
+__device__ __forceinline__ void mm_cp_async16(void* smem, const void* gmem, int bytes) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(addr), "l"(gmem), "r"(bytes) : "memory");
+}
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(MM_THREADS)
+moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ pair_of, int top,
+                    const __nv_bfloat16* __restrict__ w1, const __nv_bfloat16* __restrict__ w2, long long expert_stride,
+                    long long ldw, const int* __restrict__ tile_info, const int* __restrict__ n_tiles, int n, int k,
+                    TO* __restrict__ out, long long ldo) {
+    extern __shared__ __align__(16) unsigned char mm_raw[];
+    constexpr int STAGE = (MM_ROWS + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH;      // elements per stage
+    __nv_bfloat16* sm = reinterpret_cast<__nv_bfloat16*>(mm_raw);
+    __shared__ int src_row[MM_ROWS];
+    pdl_trigger();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= n_tiles[0]) return;
+    const int e = tile_info[3 * tile], slot0 = tile_info[3 * tile + 1], rows = tile_info[3 * tile + 2];
+    const int n0 = blockIdx.y * MM_COLS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < MM_ROWS) {
+        const int r = min(tid, rows - 1);                        // rows past the tile's end repeat its last row
+        src_row[tid] = pair_of ? pair_of[slot0 + r] / top : slot0 + r;
+    }
+    __syncthreads();
+    const __nv_bfloat16* w1e = w1 + (long long)e * expert_stride;
+    const __nv_bfloat16* w2e = GATED ? w2 + (long long)e * expert_stride : nullptr;
+
+    auto load = [&](int k0, int stage) {
+        __nv_bfloat16* sa = sm + stage * STAGE;
+        __nv_bfloat16* sb1 = sa + MM_ROWS * MM_PITCH;
+        __nv_bfloat16* sb2 = sb1 + MM_COLS * MM_PITCH;
+        {
+            const int r = tid >> 3, c = (tid & 7) * 8;
+            const int left = (k - (k0 + c)) * 2;
+            const int bytes = left >= 16 ? 16 : (left > 0 ? left : 0);
+            mm_cp_async16(sa + r * MM_PITCH + c, x + (long long)src_row[r] * ldx + (bytes ? k0 + c : 0), bytes);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * MM_THREADS;
+            const int r = idx >> 3, c = (idx & 7) * 8;
+            const int left = (k - (k0 + c)) * 2;
+            const int bytes = left >= 16 ? 16 : (left > 0 ? left : 0);
+            const long long row = min(n0 + r, n - 1);            // columns past n repeat the last one
+            mm_cp_async16(sb1 + r * MM_PITCH + c, w1e + row * ldw + (bytes ? k0 + c : 0), bytes);
+            if (GATED) mm_cp_async16(sb2 + r * MM_PITCH + c, w2e + row * ldw + (bytes ? k0 + c : 0), bytes);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float acc1[2][2][4] = {}, acc2[GATED ? 2 : 1][2][4] = {};
+    const int chunks = (k + MM_K - 1) / MM_K;
+    load(0, 0);
+    for (int ch = 0; ch < chunks; ++ch) {
+        const int stage = ch & 1;
+        if (ch + 1 < chunks) {
+            load((ch + 1) * MM_K, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const __nv_bfloat16* sa = sm + stage * STAGE;
+        const __nv_bfloat16* sb1 = sa + MM_ROWS * MM_PITCH;
+        const __nv_bfloat16* sb2 = sb1 + MM_COLS * MM_PITCH;
+        const int brow = warp * 16 + (lane & 7) + (lane >> 4) * 8, bcol = ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int kk = 0; kk < MM_K; kk += 16) {
+            uint32_t a[2][4], b[4];
+            mm_ldmatrix_x4(a[0], sa + (lane & 15) * MM_PITCH + kk + (lane >> 4) * 8);
+            mm_ldmatrix_x4(a[1], sa + (16 + (lane & 15)) * MM_PITCH + kk + (lane >> 4) * 8);
+            mm_ldmatrix_x4(b, sb1 + brow * MM_PITCH + kk + bcol);
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                mm_mma(acc1[m][0], a[m], b[0], b[1]);
+                mm_mma(acc1[m][1], a[m], b[2], b[3]);
+            }
+            if (GATED) {
+                mm_ldmatrix_x4(b, sb2 + brow * MM_PITCH + kk + bcol);
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    mm_mma(acc2[m][0], a[m], b[0], b[1]);
+                    mm_mma(acc2[m][1], a[m], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = m * 16 + g + half * 8;
+                const int col = n0 + warp * 16 + j * 8 + 2 * t4;
+                if (r >= rows || col >= n) continue;
+                float v0 = acc1[m][j][2 * half], v1 = acc1[m][j][2 * half + 1];
+                if (GATED) {
+                    v0 = v0 / (1.0f + expf(-v0)) * acc2[m][j][2 * half];
+                    v1 = v1 / (1.0f + expf(-v1)) * acc2[m][j][2 * half + 1];
+                }
+                TO* dst = out + (long long)(slot0 + r) * ldo + col;
+                dst[0] = from_float<TO>(v0);
+                if (col + 1 < n) dst[1] = from_float<TO>(v1);
+            }
+}
+
+template <typename TO, bool GATED>
+int launch_moe_mma(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, long long ldx, const int* pair_of, int top,
+                   const __nv_bfloat16* w1, const __nv_bfloat16* w2, long long expert_stride, long long ldw,
+                   const int* tile_info, const int* n_tiles, int n, int k, TO* out, long long ldo) {
+    constexpr size_t smem = 2 * (MM_ROWS + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH * sizeof(__nv_bfloat16);
+    static bool set = false;
+    if (!set) {
+        if (cudaFuncSetAttribute(moe_gemm_mma_kernel<TO, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+            return MU_ERR_LAUNCH;
+        set = true;
+    }
+    return launch_pdl(moe_gemm_mma_kernel<TO, GATED>, grid, dim3(MM_THREADS), smem, s, 1, x, ldx, pair_of, top, w1, w2,
+                      expert_stride, ldw, tile_info, n_tiles, n, k, out, ldo);
+}
+
+}  // namespace mu
+
+// As mu_moe_gemm for bfloat16 operands whose rows start on 16-byte boundaries (k, ldx, ldw multiples of 8).
+MU_EXPORT int mu_moe_gemm_mma(const void* x, long long ldx, const int* pair_of, int top, const void* w1, const void* w2,
+                              long long expert_stride, long long ldw, const int* tile_info, const int* n_tiles,
+                              int max_tiles, int n, int k, void* out, long long ldo, int out_bf16, void* stream) {
+    if (max_tiles <= 0) return MU_OK;
+    if (!x || !w1 || !tile_info || !n_tiles || !out || n <= 0 || k <= 0 || (pair_of && top <= 0))
+        return MU_ERR_BAD_ARGUMENT;
+    if (k % 8 || ldx % 8 || ldw % 8 || expert_stride % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w1 & 15) || ((uintptr_t)w2 & 15))
+        return MU_ERR_ALIGNMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(max_tiles, (n + mu::MM_COLS - 1) / mu::MM_COLS);
+    typedef __nv_bfloat16 bf;
+#define MU_MM(TO, G)                                                                                                \
+    return mu::launch_moe_mma<TO, G>(grid, s, (const bf*)x, ldx, pair_of, top, (const bf*)w1, (const bf*)w2,         \
+                                     expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo)
+    if (w2) {
+        if (out_bf16) MU_MM(bf, true);
+        MU_MM(float, true);
+    }
+    if (out_bf16) MU_MM(bf, false);
+    MU_MM(float, false);
+#undef MU_MM
+}

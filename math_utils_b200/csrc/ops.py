@@ -101,6 +101,8 @@ _SIGNATURES = {
     "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p],
     "mu_moe_gemm": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll,
                     _c_int, _c_int, _c_p],
+    "mu_moe_gemm_mma": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll,
+                        _c_int, _c_p],
     "mu_moe_combine": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_p],
     "mu_moe_tile_rows": [],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int,
@@ -433,9 +435,11 @@ def moe_group(expert_of: torch.Tensor, n_experts: int, slot_of: torch.Tensor, pa
 
 
 def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: torch.Tensor, w2: Optional[torch.Tensor],
-             tile_info: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, out: torch.Tensor) -> torch.Tensor:
+             tile_info: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, out: torch.Tensor,
+             tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """out[slot] = W1[e] x[row] (or silu(W1[e] x[row]) * W2[e] x[row] with ``w2``) for every slot of every expert e;
-    ``w1``/``w2`` [experts, n, k]; rows of ``x`` by the slot's token (``pair_of``) or by slot."""
+    ``w1``/``w2`` [experts, n, k]; rows of ``x`` by the slot's token (``pair_of``) or by slot.  bfloat16 operands
+    with 16-byte aligned rows go to the tensor cores unless ``tensor_cores`` is false."""
     _need_cuda(x, pair_of, w1, w2, tile_info, n_tiles, out)
     if w1.dim() != 3 or not w1.is_contiguous() or w1.dtype != x.dtype or x.stride(1) != 1 or x.shape[1] != w1.shape[2]:
         raise KernelError("moe_gemm takes rows [*, k] and contiguous weights [experts, n, k] of one dtype")
@@ -443,6 +447,15 @@ def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: tor
         raise KernelError("moe_gemm: the two weight stacks must agree")
     if out.stride(1) != 1 or out.shape[1] != w1.shape[1]:
         raise KernelError("moe_gemm output has the wrong shape or stride")
+    if tensor_cores is None:
+        tensor_cores = LATENT_TC
+    if (tensor_cores and x.dtype == torch.bfloat16 and w1.shape[2] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w1.data_ptr() % 16 == 0 and (w2 is None or w2.data_ptr() % 16 == 0)):
+        _check(library().mu_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(pair_of), int(top), _ptr(w1), _ptr(w2),
+                                         w1.stride(0), w1.stride(1), _ptr(tile_info), _ptr(n_tiles), int(max_tiles),
+                                         w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(out), _stream()),
+               ("moe_gemm_mma(n={}, k={})", w1.shape[1], w1.shape[2]))
+        return out
     _check(library().mu_moe_gemm(_ptr(x), x.stride(0), _ptr(pair_of), int(top), _ptr(w1), _ptr(w2),
                                  w1.stride(0), w1.stride(1), _ptr(tile_info), _ptr(n_tiles), int(max_tiles),
                                  w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(x), _is_bf16(out),

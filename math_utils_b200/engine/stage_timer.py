@@ -15,8 +15,10 @@ import torch
 
 # what the time up to each note is spent on
 STAGE_NAMES = OrderedDict([
-    ("embed", "embedding"), ("ln1", "norm 1"), ("qkv", "q | k | v product"), ("attn", "attention"),
-    ("res1", "output projection"), ("ln2", "norm 2"), ("act", "feed-forward up"), ("res2", "feed-forward down"),
+    ("embed", "embedding"), ("ln1", "norm 1"), ("qkv", "q | k | v product"),
+    ("proj", "queries | gate | latent product"), ("q_latent", "cache append, queries into latent space, rotation"),
+    ("mixed", "attention over latent rows"), ("attn", "attention"),
+    ("res1", "output projection"), ("ln2", "norm 2"), ("route", "router and grouping"), ("act", "feed-forward up"), ("res2", "feed-forward down"),
     ("lnf", "final norm"), ("logits", "output head"),
 ])
 

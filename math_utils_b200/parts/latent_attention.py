@@ -100,6 +100,7 @@ class LatentAttention(Mixer):
         n_splits, part_o, part_ml = self.splits(ctx)
         ops.latent_attention(qa, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq, H, r, self.scale,
                              mixed, n_splits, part_o, part_ml, tiles=ctx.q_tiles, single_tokens=ctx.is_decode)
+        ctx.note("mixed", mixed)
         heads = ctx.buffer("latent.heads", (T, H * self.vdim), dt)
         for i in range(H):
             self.v_up[i](mixed[:, i * r: (i + 1) * r], out=heads[:, i * self.vdim: (i + 1) * self.vdim])

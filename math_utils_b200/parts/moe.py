@@ -66,6 +66,7 @@ class RoutedExperts(FeedForward):
         ops.moe_route(h, self.router, self.correction, top, self.router_scale, expert_of, weight_of,
                       softmax=self.score == "softmax", renormalize=self.renormalize)
         ops.moe_group(expert_of, E, slot_of, pair_of, tile_info, n_tiles)
+        ctx.note("route", weight_of)
         hidden = ctx.buffer("moe.hidden", (P, self.inner_size), dt)
         ops.moe_gemm(h, pair_of, top, self.w_gate, self.w_up, tile_info, n_tiles, max_tiles, hidden)
         ctx.note("act", hidden)

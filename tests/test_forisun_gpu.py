@@ -399,9 +399,12 @@ def test_latent_append_kernel(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,tokens", [(6, 2, 70), (3, 3, 5), (5, 1, 33), (40, 4, 200), (8, 2, 1)])
-def test_routed_experts_kernels(dtype, experts, top, tokens):
+@pytest.mark.parametrize("D,F,tc", [(40, 24, False), (40, 24, True), (200, 136, True)])
+def test_routed_experts_kernels(dtype, experts, top, tokens, D, F, tc):
     ops, rng = _ops(), np.random.default_rng(6)
-    D, F, scale = 40, 24, 1.7
+    scale = 1.7
+    if tc and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core products are bfloat16")
     rnd = lambda *shape, s=1.0: dev(rng.normal(0, s, shape), dtype).float().cpu().numpy().astype(np.float64)
     h = rnd(tokens, D)
     w = {"router": rnd(experts, D, s=0.5), "correction": rng.normal(0, 0.3, experts).astype(np.float32).astype(np.float64)}
@@ -427,9 +430,9 @@ def test_routed_experts_kernels(dtype, experts, top, tokens):
     assert (np.diff(expert_of.cpu().numpy()[pair_of.cpu().numpy()]) >= 0).all()     # an expert's slots lie together
     stack = lambda k: dev(np.stack([w[f"e{e}.{k}"] for e in range(experts)]), dtype)
     hidden = torch.zeros((P, F), device="cuda", dtype=dtype)
-    ops.moe_gemm(hd, pair_of, top, stack("gate"), stack("up"), tile_info, n_tiles, max_tiles, hidden)
+    ops.moe_gemm(hd, pair_of, top, stack("gate"), stack("up"), tile_info, n_tiles, max_tiles, hidden, tensor_cores=tc)
     y = torch.zeros((P, D), device="cuda")
-    ops.moe_gemm(hidden, None, top, stack("down"), None, tile_info, n_tiles, max_tiles, y)
+    ops.moe_gemm(hidden, None, top, stack("down"), None, tile_info, n_tiles, max_tiles, y, tensor_cores=tc)
     out = torch.zeros((tokens, D), device="cuda")
     ops.moe_combine(y, slot_of, weight_of, top, out)
     assert np.abs(out.cpu().numpy() - want).max() < (3e-5 if dtype == torch.float32 else 3e-2) * max(1.0, np.abs(want).max())
