@@ -91,7 +91,8 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
 // One block.  slot_of[pair], pair_of[slot], and the tile list: tile_info[3 i] = expert, [3 i + 1] = first slot,
 // [3 i + 2] = rows; n_tiles[0] = how many.
 __global__ void moe_group_kernel(const int* __restrict__ expert_of, int n_pairs, int n_experts, int* __restrict__ slot_of,
-                                 int* __restrict__ pair_of, int* __restrict__ tile_info, int* __restrict__ n_tiles) {
+                                 int* __restrict__ pair_of, int* __restrict__ tile_info, int* __restrict__ n_tiles,
+                                 int tile_rows) {
     extern __shared__ int smi[];                       // count [n_experts], first [n_experts + 1], tile0 [n_experts + 1]
     int* count = smi;
     int* first = smi + n_experts;
@@ -108,7 +109,7 @@ __global__ void moe_group_kernel(const int* __restrict__ expert_of, int n_pairs,
             first[e] = at;
             tile0[e] = tiles;
             at += count[e];
-            tiles += (count[e] + MOE_TM - 1) / MOE_TM;
+            tiles += (count[e] + tile_rows - 1) / tile_rows;
         }
         first[n_experts] = at;
         tile0[n_experts] = tiles;
@@ -117,10 +118,10 @@ __global__ void moe_group_kernel(const int* __restrict__ expert_of, int n_pairs,
     __syncthreads();
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
         const int n = count[e];
-        for (int i = 0, k = tile0[e]; i < n; i += MOE_TM, ++k) {
+        for (int i = 0, k = tile0[e]; i < n; i += tile_rows, ++k) {
             tile_info[3 * k] = e;
             tile_info[3 * k + 1] = first[e] + i;
-            tile_info[3 * k + 2] = min(MOE_TM, n - i);
+            tile_info[3 * k + 2] = min(tile_rows, n - i);
         }
         count[e] = 0;                                  // now the cursor within the expert's slots
     }
@@ -244,15 +245,17 @@ MU_EXPORT int mu_moe_route(const void* h, long long ldh, int h_bf16, const float
                           n_tokens, hidden, n_experts, top, scale, softmax, renormalize, expert_of, weight_of);
 }
 
-// tile_info needs 3 * (n_pairs / tile_rows + n_experts) ints.
+// tile_info needs 3 * (n_pairs / tile_rows + n_experts) ints.  tile_rows: the CUDA-core product takes tiles of
+// mu_moe_tile_rows() slots, the tensor-core product of 32 or 64.
 MU_EXPORT int mu_moe_group(const int* expert_of, int n_pairs, int n_experts, int* slot_of, int* pair_of, int* tile_info,
-                           int* n_tiles, void* stream) {
+                           int* n_tiles, int tile_rows, void* stream) {
     if (n_pairs <= 0) return MU_OK;
-    if (!expert_of || !slot_of || !pair_of || !tile_info || !n_tiles || n_experts <= 0) return MU_ERR_BAD_ARGUMENT;
+    if (!expert_of || !slot_of || !pair_of || !tile_info || !n_tiles || n_experts <= 0 || tile_rows <= 0)
+        return MU_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)(3 * n_experts + 2) * sizeof(int);
     if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
     return mu::launch_pdl(mu::moe_group_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, 1, expert_of, n_pairs,
-                          n_experts, slot_of, pair_of, tile_info, n_tiles);
+                          n_experts, slot_of, pair_of, tile_info, n_tiles, tile_rows);
 }
 
 // w1 (and w2 when gated): [n_experts][n][k] with row stride ldw and expert stride `expert_stride` elements.

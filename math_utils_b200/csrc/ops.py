@@ -98,11 +98,13 @@ _SIGNATURES = {
                                 _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p],
     "mu_moe_route": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p,
                      _c_p],
-    "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p],
+    "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
     "mu_moe_gemm": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll,
                     _c_int, _c_int, _c_p],
-    "mu_moe_gemm_mma": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll,
-                        _c_int, _c_p],
+    "mu_moe_gemm_mma": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p,
+                        _c_ll, _c_int, _c_p],
+    "mu_heads_gemm": [_c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_ll, _c_int,
+                      _c_p],
     "mu_moe_combine": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_p],
     "mu_moe_tile_rows": [],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int,
@@ -423,23 +425,31 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
                                   _ptr(weight_of), _stream()), ("moe_route(experts={}, top={})", n_experts, top))
 
 
+def moe_tc_ok(x_dtype: torch.dtype, k1: int, k2: int) -> bool:
+    """Whether the experts' products of a bfloat16 layer go to the tensor cores (both inner sizes multiples of 8)."""
+    return LATENT_TC and x_dtype == torch.bfloat16 and k1 % 8 == 0 and k2 % 8 == 0
+
+
 def moe_group(expert_of: torch.Tensor, n_experts: int, slot_of: torch.Tensor, pair_of: torch.Tensor,
-              tile_info: torch.Tensor, n_tiles: torch.Tensor) -> None:
-    """Groups the (token, expert) pairs by expert: a slot per pair, and the list of row tiles per expert."""
+              tile_info: torch.Tensor, n_tiles: torch.Tensor, tile_rows: int = 0) -> None:
+    """Groups the (token, expert) pairs by expert: a slot per pair, and the list of tiles of up to ``tile_rows``
+    slots per expert (0: the CUDA-core product's tile)."""
     _need_cuda(expert_of, slot_of, pair_of, tile_info, n_tiles)
     for t, name in ((expert_of, "expert_of"), (slot_of, "slot_of"), (pair_of, "pair_of"), (tile_info, "tile_info"),
                     (n_tiles, "n_tiles")):
         _i32(t, name)
     _check(library().mu_moe_group(_ptr(expert_of), expert_of.numel(), int(n_experts), _ptr(slot_of), _ptr(pair_of),
-                                  _ptr(tile_info), _ptr(n_tiles), _stream()), "moe_group")
+                                  _ptr(tile_info), _ptr(n_tiles), int(tile_rows) or moe_tile_rows(), _stream()),
+           "moe_group")
 
 
 def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: torch.Tensor, w2: Optional[torch.Tensor],
              tile_info: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, out: torch.Tensor,
-             tensor_cores: Optional[bool] = None) -> torch.Tensor:
+             tensor_cores: Optional[bool] = None, tile_rows: int = 0) -> torch.Tensor:
     """out[slot] = W1[e] x[row] (or silu(W1[e] x[row]) * W2[e] x[row] with ``w2``) for every slot of every expert e;
     ``w1``/``w2`` [experts, n, k]; rows of ``x`` by the slot's token (``pair_of``) or by slot.  bfloat16 operands
-    with 16-byte aligned rows go to the tensor cores unless ``tensor_cores`` is false."""
+    with 16-byte aligned rows go to the tensor cores unless ``tensor_cores`` is false.  ``tile_rows``: what
+    ``moe_group`` was given (the CUDA-core product takes its own tile only)."""
     _need_cuda(x, pair_of, w1, w2, tile_info, n_tiles, out)
     if w1.dim() != 3 or not w1.is_contiguous() or w1.dtype != x.dtype or x.stride(1) != 1 or x.shape[1] != w1.shape[2]:
         raise KernelError("moe_gemm takes rows [*, k] and contiguous weights [experts, n, k] of one dtype")
@@ -449,17 +459,39 @@ def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: tor
         raise KernelError("moe_gemm output has the wrong shape or stride")
     if tensor_cores is None:
         tensor_cores = LATENT_TC
+    tile_rows = int(tile_rows) or moe_tile_rows()
     if (tensor_cores and x.dtype == torch.bfloat16 and w1.shape[2] % 8 == 0 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w1.data_ptr() % 16 == 0 and (w2 is None or w2.data_ptr() % 16 == 0)):
         _check(library().mu_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(pair_of), int(top), _ptr(w1), _ptr(w2),
                                          w1.stride(0), w1.stride(1), _ptr(tile_info), _ptr(n_tiles), int(max_tiles),
-                                         w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(out), _stream()),
-               ("moe_gemm_mma(n={}, k={})", w1.shape[1], w1.shape[2]))
+                                         tile_rows, w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(out),
+                                         _stream()), ("moe_gemm_mma(n={}, k={})", w1.shape[1], w1.shape[2]))
         return out
+    if tile_rows != moe_tile_rows():
+        raise KernelError(f"the CUDA-core experts' product takes tiles of {moe_tile_rows()} slots, got {tile_rows}")
     _check(library().mu_moe_gemm(_ptr(x), x.stride(0), _ptr(pair_of), int(top), _ptr(w1), _ptr(w2),
                                  w1.stride(0), w1.stride(1), _ptr(tile_info), _ptr(n_tiles), int(max_tiles),
                                  w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(x), _is_bf16(out),
                                  _stream()), ("moe_gemm(n={}, k={})", w1.shape[1], w1.shape[2]))
+    return out
+
+
+def heads_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: int, out_head_stride: int) -> torch.Tensor:
+    """out[t, h, :] = W[h] x[t, h, :] for every row t and head h: ``w`` [heads, n, k]; ``x`` / ``out`` views whose first
+    element is head 0's first entry, a head's slice ``x_head_stride`` / ``out_head_stride`` elements after the head
+    before.  bfloat16 operands with aligned slices run as ONE launch on the tensor cores; anything else head by head
+    through ``linear``."""
+    _need_cuda(x, w, out)
+    heads, n, k = w.shape
+    if (LATENT_TC and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and k % 8 == 0
+            and x.stride(0) % 8 == 0 and x_head_stride % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and x.stride(1) == 1 and out.stride(1) == 1):
+        _check(library().mu_heads_gemm(_ptr(x), x.stride(0), int(x_head_stride), _ptr(w), w.stride(0), w.stride(1),
+                                       x.shape[0], heads, n, k, _ptr(out), out.stride(0), int(out_head_stride),
+                                       _is_bf16(out), _stream()), ("heads_gemm(heads={}, n={}, k={})", heads, n, k))
+        return out
+    for h in range(heads):
+        linear(x[:, h * x_head_stride: h * x_head_stride + k], w[h], out=out[:, h * out_head_stride: h * out_head_stride + n])
     return out
 
 

@@ -67,10 +67,8 @@ class LatentAttention(Mixer):
         self.proj = Linear(torch.cat(parts, dim=0).contiguous(), None, runtime)
         self.norm_weight = t("dkv_norm") if self.own_kv else None
         # U_h^T as [kv_rank, dim] per head ([out, in] for the product that carries a query into latent space)
-        uk = t("uk").reshape(H, self.dim, self.kv_rank)
-        self.q_up = [Linear(uk[h].t().contiguous(), None, runtime) for h in range(H)]
-        uv = t("uv").reshape(H, self.vdim, self.kv_rank)
-        self.v_up = [Linear(uv[h].contiguous(), None, runtime) for h in range(H)]
+        self.q_up = t("uk").reshape(H, self.dim, self.kv_rank).transpose(1, 2).contiguous()      # [H, kv_rank, dim]
+        self.v_up = t("uv").reshape(H, self.vdim, self.kv_rank).contiguous()                     # [H, vdim, kv_rank]
         self.out = Linear(t("out"), None, runtime)
         # (one entry at least, so that the kernels always get a table)
         self.freq_table = torch.tensor(self.freqs or [0.0], dtype=torch.float64).to(torch.float32).to(runtime.device)
@@ -90,8 +88,7 @@ class LatentAttention(Mixer):
                               r, self.rot_dim, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens, cache.pages)
         # queries in latent space, float32: [T, H, kv_rank | rot_dim]
         qa = ctx.buffer("latent.q", (T, H * self.row), torch.float32)
-        for i in range(H):
-            self.q_up[i](q[:, i * self.q_head: i * self.q_head + self.dim], out=qa[:, i * self.row: i * self.row + r])
+        ops.heads_gemm(q, self.q_up, qa, self.q_head, self.row)
         if self.rot_dim:
             ops.rotary(q[:, self.dim:], qa[:, r:], ctx.tok_pos, self.freq_table, self.magnitude, H, self.rot_dims,
                        self.rot_dim, self.q_head, self.row)
@@ -102,8 +99,7 @@ class LatentAttention(Mixer):
                              mixed, n_splits, part_o, part_ml, tiles=ctx.q_tiles, single_tokens=ctx.is_decode)
         ctx.note("mixed", mixed)
         heads = ctx.buffer("latent.heads", (T, H * self.vdim), dt)
-        for i in range(H):
-            self.v_up[i](mixed[:, i * r: (i + 1) * r], out=heads[:, i * self.vdim: (i + 1) * self.vdim])
+        ops.heads_gemm(mixed, self.v_up, heads, r, self.vdim)
         ops.sigmoid_gate(heads, gate)
         ctx.note("attn", heads)
         self.out(heads, residual=residual if accumulate else None, out=residual)

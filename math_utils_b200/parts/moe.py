@@ -58,20 +58,24 @@ class RoutedExperts(FeedForward):
         ops, dt = self.runtime.ops, self.runtime.dtype
         T, top, E = ctx.n_tokens, self.top, self.n_experts
         P = T * top
-        max_tiles = P // self.tile_rows + E                # every grouping of P pairs into E experts fits
+        # tiles of 64 slots where the tensor cores take the products and an expert has the rows to fill them
+        tile_rows = self.tile_rows
+        if ops.moe_tc_ok(dt, self.hidden_size, self.inner_size) and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0:
+            tile_rows = 64 if P >= 48 * E else 32
+        max_tiles = P // tile_rows + E                     # every grouping of P pairs into E experts fits
         index = ctx.buffer("moe.index", (3 * P + 3 * max_tiles + 4,), torch.int32)
         expert_of, slot_of, pair_of = index[:P], index[P:2 * P], index[2 * P:3 * P]
         tile_info, n_tiles = index[3 * P: 3 * P + 3 * max_tiles], index[3 * P + 3 * max_tiles:]
         weight_of = ctx.buffer("moe.weight", (P,), torch.float32)
         ops.moe_route(h, self.router, self.correction, top, self.router_scale, expert_of, weight_of,
                       softmax=self.score == "softmax", renormalize=self.renormalize)
-        ops.moe_group(expert_of, E, slot_of, pair_of, tile_info, n_tiles)
+        ops.moe_group(expert_of, E, slot_of, pair_of, tile_info, n_tiles, tile_rows)
         ctx.note("route", weight_of)
         hidden = ctx.buffer("moe.hidden", (P, self.inner_size), dt)
-        ops.moe_gemm(h, pair_of, top, self.w_gate, self.w_up, tile_info, n_tiles, max_tiles, hidden)
+        ops.moe_gemm(h, pair_of, top, self.w_gate, self.w_up, tile_info, n_tiles, max_tiles, hidden, tile_rows=tile_rows)
         ctx.note("act", hidden)
         y = ctx.buffer("moe.out", (P, self.hidden_size), torch.float32)
-        ops.moe_gemm(hidden, None, top, self.w_down, None, tile_info, n_tiles, max_tiles, y)
+        ops.moe_gemm(hidden, None, top, self.w_down, None, tile_info, n_tiles, max_tiles, y, tile_rows=tile_rows)
         if accumulate:
             mixed = ctx.buffer("moe.mixed", (T, self.hidden_size), torch.float32)
             ops.moe_combine(y, slot_of, weight_of, top, mixed)

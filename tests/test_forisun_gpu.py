@@ -399,7 +399,7 @@ def test_latent_append_kernel(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,tokens", [(6, 2, 70), (3, 3, 5), (5, 1, 33), (40, 4, 200), (8, 2, 1)])
-@pytest.mark.parametrize("D,F,tc", [(40, 24, False), (40, 24, True), (200, 136, True)])
+@pytest.mark.parametrize("D,F,tc", [(40, 24, 0), (40, 24, 32), (200, 136, 32), (200, 136, 64)])
 def test_routed_experts_kernels(dtype, experts, top, tokens, D, F, tc):
     ops, rng = _ops(), np.random.default_rng(6)
     scale = 1.7
@@ -413,7 +413,7 @@ def test_routed_experts_kernels(dtype, experts, top, tokens, D, F, tc):
     mlp = {"router": {"experts": experts, "top": top, "scale": scale}}
     want = plain.routed_ff(h, mlp, w, "")
     P = tokens * top
-    max_tiles = P // ops.moe_tile_rows() + experts
+    max_tiles = P // (tc or ops.moe_tile_rows()) + experts
     expert_of, slot_of, pair_of = (torch.zeros(P, dtype=torch.int32, device="cuda") for _ in range(3))
     tile_info = torch.zeros(3 * max_tiles, dtype=torch.int32, device="cuda")
     n_tiles = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -424,15 +424,15 @@ def test_routed_experts_kernels(dtype, experts, top, tokens, D, F, tc):
     choice = np.argsort(-(s + w["correction"]), axis=1, kind="stable")[:, :top]
     assert (expert_of.cpu().numpy().reshape(tokens, top) == choice).all()
     assert np.abs(weight_of.cpu().numpy().reshape(tokens, top) - np.take_along_axis(s, choice, 1) * scale).max() < 1e-5
-    ops.moe_group(expert_of, experts, slot_of, pair_of, tile_info, n_tiles)
+    ops.moe_group(expert_of, experts, slot_of, pair_of, tile_info, n_tiles, tc)
     slots = slot_of.cpu().numpy()
     assert sorted(slots.tolist()) == list(range(P)) and (pair_of.cpu().numpy()[slots] == np.arange(P)).all()
     assert (np.diff(expert_of.cpu().numpy()[pair_of.cpu().numpy()]) >= 0).all()     # an expert's slots lie together
     stack = lambda k: dev(np.stack([w[f"e{e}.{k}"] for e in range(experts)]), dtype)
     hidden = torch.zeros((P, F), device="cuda", dtype=dtype)
-    ops.moe_gemm(hd, pair_of, top, stack("gate"), stack("up"), tile_info, n_tiles, max_tiles, hidden, tensor_cores=tc)
+    ops.moe_gemm(hd, pair_of, top, stack("gate"), stack("up"), tile_info, n_tiles, max_tiles, hidden, tensor_cores=bool(tc), tile_rows=tc)
     y = torch.zeros((P, D), device="cuda")
-    ops.moe_gemm(hidden, None, top, stack("down"), None, tile_info, n_tiles, max_tiles, y, tensor_cores=tc)
+    ops.moe_gemm(hidden, None, top, stack("down"), None, tile_info, n_tiles, max_tiles, y, tensor_cores=bool(tc), tile_rows=tc)
     out = torch.zeros((tokens, D), device="cuda")
     ops.moe_combine(y, slot_of, weight_of, top, out)
     assert np.abs(out.cpu().numpy() - want).max() < (3e-5 if dtype == torch.float32 else 3e-2) * max(1.0, np.abs(want).max())
@@ -444,3 +444,22 @@ def test_sigmoid_gate_kernel():
     od = dev(o)
     ops.sigmoid_gate(od, dev(g))
     assert np.abs(od.cpu().numpy() - o * plain.sigmoid(g)).max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                            (torch.float32, torch.float32)])
+@pytest.mark.parametrize("rows,heads,n,k,lead", [(1, 3, 64, 16, 8), (70, 6, 128, 32, 32), (33, 2, 24, 200, 0), (5, 4, 10, 12, 3)])
+def test_products_per_head(dtype, out_dtype, rows, heads, n, k, lead):
+    """out[t, h] = W[h] x[t, h]: the heads' slices sit `lead` entries apart from one another's ends."""
+    ops, rng = _ops(), np.random.default_rng(9)
+    xs, os_ = k + lead, n + 5 + (n + 5) % 2
+    x = dev(rng.normal(0, 1, (rows, heads * xs)), dtype)
+    w = dev(rng.normal(0, 1, (heads, n, k)) / math.sqrt(k), dtype)
+    out = torch.zeros((rows, heads * os_), device="cuda", dtype=out_dtype)
+    ops.heads_gemm(x, w, out, xs, os_)
+    xf, wf = x.float().cpu().numpy().astype(np.float64), w.float().cpu().numpy().astype(np.float64)
+    got = out.float().cpu().numpy().reshape(rows, heads, os_)
+    for h in range(heads):
+        want = xf[:, h * xs: h * xs + k] @ wf[h].T
+        assert np.abs(got[:, h, :n] - want).max() < (2e-5 if out_dtype == torch.float32 else 3e-2)
+        assert not got[:, h, n:].any()                                      # nothing written between the slices
