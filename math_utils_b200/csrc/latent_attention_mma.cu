@@ -30,6 +30,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(addr), "l"(gmem) : "memory");
@@ -93,15 +98,12 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
     const int per = (n_pages + n_splits - 1) / n_splits;
     const int p_lo = blockIdx.y * per, p_hi = min(n_pages, p_lo + per);
     const int* pages = block_table + (long long)tok_seq[first] * max_pages;
-    const int chunks_per_row = width / 8;
 
     auto load_page = [&](int p, int buf) {
         const __nv_bfloat16* src = rows + (long long)pages[p] * LM_KEYS * width;
         __nv_bfloat16* dst = Ks + buf * LM_KEYS * w8;
-        for (int c = tid; c < LM_KEYS * chunks_per_row; c += LM_THREADS) {
-            const int r = c / chunks_per_row, o = (c % chunks_per_row) * 8;
-            cp_async16(dst + r * w8 + o, src + (long long)r * width + o);
-        }
+        for (int r = warp; r < LM_KEYS; r += LM_THREADS / 32)       // a warp a row, lanes along it: no division
+            for (int o = lane * 8; o < width; o += 256) cp_async16(dst + r * w8 + o, src + r * width + o);
         cp_async_commit();
     };
 
@@ -124,17 +126,16 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
         const __nv_bfloat16* K = Ks + buf * LM_KEYS * w8;
         // ---- S = Q K^T for rows rg * 16 .. + 16 and keys g * 16 .. + 16
         float s[2][4] = {};
-        const __nv_bfloat16* qa = Qs + ra * w8 + 2 * t4;
-        const __nv_bfloat16* qb = Qs + rb * w8 + 2 * t4;
-        const __nv_bfloat16* k0p = K + (g * 16 + gq) * w8 + 2 * t4;
-        const __nv_bfloat16* k1p = k0p + 8 * w8;
+        // fragments by ldmatrix: Q rows rg * 16 .. (row-major, k along the row), K rows = keys g * 16 .. (the same)
+        const __nv_bfloat16* qf = Qs + (rg * 16 + (lane & 15)) * w8 + (lane >> 4) * 8;
+        const __nv_bfloat16* kf = K + (g * 16 + (lane & 7) + (lane >> 4) * 8) * w8 + ((lane >> 3) & 1) * 8;
+#pragma unroll 4
         for (int k0 = 0; k0 < width; k0 += 16) {
-            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + k0), a1 = *reinterpret_cast<const uint32_t*>(qb + k0);
-            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + k0 + 8), a3 = *reinterpret_cast<const uint32_t*>(qb + k0 + 8);
-            mma_bf16(s[0], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k0p + k0),
-                     *reinterpret_cast<const uint32_t*>(k0p + k0 + 8));
-            mma_bf16(s[1], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k1p + k0),
-                     *reinterpret_cast<const uint32_t*>(k1p + k0 + 8));
+            uint32_t a[4], b[4];
+            ldmatrix_x4(a, qf + k0);
+            ldmatrix_x4(b, kf + k0);
+            mma_bf16(s[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+            mma_bf16(s[1], a[0], a[1], a[2], a[3], b[2], b[3]);
         }
         const int pos_a = row_pos[ra], pos_b = row_pos[rb];
         float top_a = -INFINITY, top_b = -INFINITY;
