@@ -469,7 +469,8 @@ def forisun_config(size):
     moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top, "scale": 2.5}}
     layers = [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": dense} if i == 0 else moe}
               for i in range(L)]
-    ours = {"architecture": "Forisun", "vocab": FAMILY_VOCAB, "width": D, "embedding": {"scale": 1.0},
+    # the embedding scale brings the random table's rows to order one, so that tokens differ where the router looks
+    ours = {"architecture": "Forisun", "vocab": FAMILY_VOCAB, "width": D, "embedding": {"scale": float(D) ** 0.5},
             "norm": {"eps": 1e-5}, "layers": layers}
     twin = {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "n_layer": L, "n_embd": D, "n_head": D // 64,
             "n_inner": top * ff * 3 // 2, "vocab_size": FAMILY_VOCAB, "n_positions": CONTEXT,
