@@ -465,8 +465,8 @@ def forisun_config(size):
     work per token (a gated expert has three matrices where GPT-2's feed-forward has two), head size 64."""
     D, H, dn, dr, dv, r, E, top, ff, dense, L = FORISUN_SIZES[size]
     mixer = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": (dn + dr) ** -0.5,
-             "rot": {"base": 10000.0, "dims": dr, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
-    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top, "scale": 2.5}}
+             "rot": {"base": 10000.0, "dims": dr, "scaling": {"factor": 4.0, "original": 1024, "fast": 16.0, "slow": 2.0}}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top, "scale": 2.0}}
     layers = [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": dense} if i == 0 else moe}
               for i in range(L)]
     # the embedding scale brings the random table's rows to order one, so that tokens differ where the router looks

@@ -68,7 +68,7 @@ def test_random_model_folder_round_trips(tmp_path):
     assert tuple(f.read("l0.norm1.alpha").shape) == ()
 
 
-@pytest.mark.parametrize("rot", [ROT, {"base": 1e6, "dims": 32, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+@pytest.mark.parametrize("rot", [ROT, {"base": 2e5, "dims": 24, "scaling": {"factor": 6.0, "original": 4096, "fast": 24.0, "slow": 2.0}},
                                  {"base": 100.0, "dims": 4}, {"base": 10.0, "dims": 0}])
 def test_frequency_tables(rot):
     freqs, mag = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))

@@ -51,10 +51,10 @@ CFG_B = {"architecture": "Forisun", "vocab": 131, "width": 50, "embedding": {"sc
                     layer(_B1, moe(3, 3, 10, 0.9)),
                     layer(dict(_B1, heads=2, dim=9, vdim=11, kv_from=1), moe(5, 1, 14, 2.0))]}
 # sizes the tensor-core products take
-_C = mixer(4, 32, 16, 32, 64, 0.15, base=1.0e6, scaling={"factor": 8.0, "original": 128, "fast": 32.0, "slow": 1.0})
-CFG_C = {"architecture": "Forisun", "vocab": 512, "width": 128, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
-         "layers": [layer(_C, {"kind": "dense", "ff": 256}), layer(_C, moe(8, 2, 64, 2.5)),
-                    layer(dict(_C, kv_from=1), moe(8, 2, 64, 2.5))]}
+_C = mixer(4, 32, 16, 32, 64, 0.15, base=5.0e5, scaling={"factor": 5.0, "original": 128, "fast": 20.0, "slow": 1.5})
+CFG_C = {"architecture": "Forisun", "vocab": 384, "width": 128, "embedding": {"scale": 1.0}, "norm": {"eps": 2e-5},
+         "layers": [layer(_C, {"kind": "dense", "ff": 256}), layer(_C, moe(8, 2, 64, 1.8)),
+                    layer(dict(_C, kv_from=1), moe(8, 2, 64, 1.8))]}
 CONFIGS = {"a": CFG_A, "b": CFG_B, "c": CFG_C}
 
 
@@ -256,7 +256,7 @@ def test_rms_norm_kernel():
         assert np.abs(ops.rms_norm(dev(x), dev(w), eps).cpu().numpy() - want).max() < 3e-6
 
 
-@pytest.mark.parametrize("scaling", [None, YARN, {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}])
+@pytest.mark.parametrize("scaling", [None, YARN, {"factor": 6.0, "original": 1024, "fast": 24.0, "slow": 2.0}])
 @pytest.mark.parametrize("dims,width", [(8, 8), (4, 10), (32, 32)])
 def test_rotary_kernel(scaling, dims, width):
     ops, rng = _ops(), np.random.default_rng(3)
@@ -306,7 +306,7 @@ def _plain_latent(q, rows, kv_rank, scale):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(3, 32, 8), (1, 12, 6), (4, 128, 32), (2, 200, 24)])
+@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(3, 32, 8), (1, 12, 6), (4, 128, 48), (2, 200, 24)])
 @pytest.mark.parametrize("n_splits", [1, 3, 7])
 def test_latent_attention_kernel(dtype, heads, kv_rank, rot_dim, n_splits):
     ops, rng = _ops(), np.random.default_rng(4)
@@ -344,7 +344,7 @@ def test_latent_attention_kernel(dtype, heads, kv_rank, rot_dim, n_splits):
         assert np.abs(got[5, 0] - seqs[5][far, :kv_rank]).max() < 0.5 * abs(seqs[5][far, :kv_rank]).max()
 
 
-@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(3, 64, 16), (6, 128, 32), (16, 256, 32), (40, 64, 0), (2, 512, 64)])
+@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(3, 64, 16), (6, 128, 16), (16, 256, 32), (40, 64, 0), (2, 512, 64)])
 def test_latent_attention_on_tensor_cores_prompt_tiles(heads, kv_rank, rot_dim):
     """Whole prompts of several sequences in one step: tiles of up to 64 tokens, every token its own causal edge."""
     ops, rng = _ops(), np.random.default_rng(8)
