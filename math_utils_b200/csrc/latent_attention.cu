@@ -52,17 +52,43 @@ __global__ void rotary_kernel(const TI* __restrict__ x, long long ldx, int x_hea
     }
 }
 
+// With q (and qa): the same block also rotates the token's queries (every head's rot_dim entries at q + h *
+// q_head_stride) into qa + h * qa_head_stride as float32, so that a step needs one launch for both.  With dkv
+// null only the queries are rotated (a layer that reads another layer's cache).
 template <typename T>
 __global__ void latent_append_kernel(const T* __restrict__ dkv, long long ld, const float* __restrict__ norm_w, float eps,
                                      const float* __restrict__ freqs, float mag, int rot_dims, int kv_rank, int rot_dim,
                                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                      const int* __restrict__ block_table, int max_pages, int page_tokens,
-                                     T* __restrict__ rows) {
+                                     T* __restrict__ rows, const T* __restrict__ q, long long ldq, int q_head_stride,
+                                     float* __restrict__ qa, long long ldqa, int qa_head_stride, int n_heads) {
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     const int p = tok_pos[t];
+    if (q) {
+        const int half = rot_dims / 2, per_head = rot_dim - half;
+        const float pos = (float)p;
+        const T* src = q + (long long)t * ldq;
+        float* dst = qa + (long long)t * ldqa;
+        for (int i = threadIdx.x; i < n_heads * per_head; i += blockDim.x) {
+            const int h = i / per_head, e = i % per_head;
+            const T* s = src + (long long)h * q_head_stride;
+            float* d = dst + (long long)h * qa_head_stride;
+            if (e < half) {
+                float sn, cs;
+                sincosf(pos * freqs[e], &sn, &cs);
+                sn *= mag; cs *= mag;
+                const float u = to_float(s[e]), v = to_float(s[e + half]);
+                d[e] = u * cs - v * sn;
+                d[e + half] = v * cs + u * sn;
+            } else {
+                d[e + half] = to_float(s[e + half]);
+            }
+        }
+    }
+    if (!dkv) return;
     const long long page = block_table[(long long)tok_seq[t] * max_pages + p / page_tokens];
     const int width = kv_rank + rot_dim;
     T* dst = rows + (page * page_tokens + p % page_tokens) * width;
@@ -184,6 +210,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
                                     int kv_rank, int n_splits, T* __restrict__ out, long long ldo) {
     pdl_trigger();
     pdl_wait();
+    __shared__ float factor[64];                       // the parts' weights, 64 parts at a time
     const int item = blockIdx.x, t = item / n_heads;
     const float* ml = part_ml + (long long)item * n_splits * 2;
     float top = -INFINITY;
@@ -192,11 +219,28 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
     for (int s = 0; s < n_splits; ++s) sum += ml[2 * s] == -INFINITY ? 0.0f : ml[2 * s + 1] * expf(ml[2 * s] - top);
     const float inv = 1.0f / sum;
     T* dst = out + (long long)t * ldo + (long long)(item % n_heads) * kv_rank;
-    for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
-        float v = 0.0f;
-        for (int s = 0; s < n_splits; ++s)
-            if (ml[2 * s] != -INFINITY) v += part_o[((long long)item * n_splits + s) * kv_rank + d] * expf(ml[2 * s] - top);
-        dst[d] = from_float<T>(v * inv);
+    constexpr int MAX_D = 8;                           // output entries a thread keeps (kv_rank <= 8 * blockDim.x)
+    float v[MAX_D] = {};
+    for (int s0 = 0; s0 < n_splits; s0 += 64) {
+        __syncthreads();
+        if (threadIdx.x < 64 && s0 + threadIdx.x < n_splits) {
+            const float m = ml[2 * (s0 + threadIdx.x)];
+            factor[threadIdx.x] = m == -INFINITY ? 0.0f : expf(m - top);
+        }
+        __syncthreads();
+        const int n = min(64, n_splits - s0);
+#pragma unroll
+        for (int i = 0; i < MAX_D; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            if (d < kv_rank)
+                for (int s = 0; s < n; ++s)
+                    if (factor[s] != 0.0f) v[i] += part_o[((long long)item * n_splits + s0 + s) * kv_rank + d] * factor[s];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_D; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+        if (d < kv_rank) dst[d] = from_float<T>(v[i] * inv);
     }
 }
 
@@ -245,23 +289,26 @@ MU_EXPORT int mu_rotary(const void* x, long long ldx, int x_head_stride, int x_b
 #undef MU_ROT
 }
 
+// dkv may be null (no cache row is written) if q is given; q may be null (no queries are rotated).
 MU_EXPORT int mu_latent_append(const void* dkv, long long ld, const float* norm_w, float eps, const float* freqs,
                                float mag, int rot_dims, int kv_rank, int rot_dim, const int* tok_pos,
                                const int* tok_seq, const int* block_table, int max_pages, int page_tokens,
-                               int n_tokens, void* rows, int is_bf16, void* stream) {
+                               int n_tokens, void* rows, int is_bf16, const void* q, long long ldq, int q_head_stride,
+                               float* qa, long long ldqa, int qa_head_stride, int n_heads, void* stream) {
     if (n_tokens <= 0) return MU_OK;
-    if (!dkv || !norm_w || !freqs || !tok_pos || !tok_seq || !block_table || !rows || kv_rank <= 0 || rot_dim < 0 ||
-        rot_dims % 2 || rot_dims > rot_dim || page_tokens <= 0)
+    if ((!dkv && !q) || !freqs || !tok_pos || kv_rank <= 0 || rot_dim < 0 || rot_dims % 2 || rot_dims > rot_dim ||
+        (dkv && (!norm_w || !tok_seq || !block_table || !rows || page_tokens <= 0)) || (q && (!qa || n_heads <= 0)))
         return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(n_tokens), block(kv_rank >= 512 ? 256 : 128);
     if (is_bf16)
         return mu::launch_pdl(mu::latent_append_kernel<__nv_bfloat16>, grid, block, 0, s, 1, (const __nv_bfloat16*)dkv,
                               ld, norm_w, eps, freqs, mag, rot_dims, kv_rank, rot_dim, tok_pos, tok_seq, block_table,
-                              max_pages, page_tokens, (__nv_bfloat16*)rows);
+                              max_pages, page_tokens, (__nv_bfloat16*)rows, (const __nv_bfloat16*)q, ldq, q_head_stride,
+                              qa, ldqa, qa_head_stride, n_heads);
     return mu::launch_pdl(mu::latent_append_kernel<float>, grid, block, 0, s, 1, (const float*)dkv, ld, norm_w, eps,
                           freqs, mag, rot_dims, kv_rank, rot_dim, tok_pos, tok_seq, block_table, max_pages, page_tokens,
-                          (float*)rows);
+                          (float*)rows, (const float*)q, ldq, q_head_stride, qa, ldqa, qa_head_stride, n_heads);
 }
 
 // q: float32 [n_tokens, n_heads, width]; out: [n_tokens, ldo] with head h at columns h * kv_rank.
@@ -286,7 +333,7 @@ MU_EXPORT int mu_latent_attention(const float* q, const void* rows, const int* b
                                                tok_seq, n_tokens, n_heads, kv_rank, width, scale, n_splits, (float*)out,
                                                ldo, part_o, part_ml, s);
     if (code != MU_OK || n_splits == 1) return code;
-    const dim3 grid(n_tokens * n_heads), block(128);
+    const dim3 grid(n_tokens * n_heads), block(kv_rank > 1024 ? 512 : 128);    // a thread keeps up to 8 entries
     if (is_bf16)
         return mu::launch_pdl(mu::latent_merge_kernel<__nv_bfloat16>, grid, block, 0, s, 1, (const float*)part_o,
                               (const float*)part_ml, n_heads, kv_rank, n_splits, (__nv_bfloat16*)out, ldo);
@@ -300,7 +347,7 @@ MU_EXPORT int mu_latent_merge(const float* part_o, const float* part_ml, int n_t
     if (n_tokens <= 0) return MU_OK;
     if (!part_o || !part_ml || !out || n_heads <= 0 || kv_rank <= 0 || n_splits < 1) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_tokens * n_heads), block(128);
+    const dim3 grid(n_tokens * n_heads), block(kv_rank > 1024 ? 512 : 128);    // a thread keeps up to 8 entries
     if (is_bf16)
         return mu::launch_pdl(mu::latent_merge_kernel<__nv_bfloat16>, grid, block, 0, s, 1, part_o, part_ml, n_heads,
                               kv_rank, n_splits, (__nv_bfloat16*)out, ldo);

@@ -21,7 +21,7 @@ namespace mu {
 
 constexpr int MOE_TM = 32, MOE_TN = 64, MOE_TK = 32;
 
-constexpr int ROUTE_WARPS = 8;
+constexpr int ROUTE_WARPS = 16;
 
 // One block per token: the token's row is staged in shared memory as float32, the warps share the experts (each
 // logit one warp's sum over the row, lanes striding along it), then the first warp scores and chooses.
@@ -31,7 +31,7 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
                  const float* __restrict__ correction, int n_tokens, int hidden, int n_experts, int top,
                  float scale, int softmax, int renormalize, int* __restrict__ expert_of,
                  float* __restrict__ weight_of) {
-    extern __shared__ float sm[];                      // row [hidden], scores [n_experts], choice [n_experts]
+    extern __shared__ __align__(16) float sm[];        // row [hidden], scores [n_experts], choice [n_experts]
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -42,10 +42,23 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
     const T* row = h + (long long)t * ldh;
     for (int d = threadIdx.x; d < hidden; d += blockDim.x) hrow[d] = to_float(row[d]);
     __syncthreads();
+    const bool wide = hidden % 4 == 0 && ((uintptr_t)router & 15) == 0;      // rows of the router in 16-byte pieces
     for (int e = warp; e < n_experts; e += ROUTE_WARPS) {
         const float* w = router + (long long)e * hidden;
         float z = 0.0f;
-        for (int d = lane; d < hidden; d += 32) z += hrow[d] * w[d];
+        if (wide) {
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* h4 = reinterpret_cast<const float4*>(hrow);
+            float z0 = 0.0f, z1 = 0.0f, z2 = 0.0f, z3 = 0.0f;             // the lane's sum in four parts, then in order
+#pragma unroll 4
+            for (int d = lane; d < hidden / 4; d += 32) {
+                const float4 a = h4[d], b = w4[d];
+                z0 += a.x * b.x; z1 += a.y * b.y; z2 += a.z * b.z; z3 += a.w * b.w;
+            }
+            z = (z0 + z1) + (z2 + z3);
+        } else {
+            for (int d = lane; d < hidden; d += 32) z += hrow[d] * w[d];
+        }
         z = warp_sum(z);
         if (lane == 0) score[e] = z;
     }
@@ -223,7 +236,33 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long long ldy, c
     }
 }
 
+// The same sum, normed and added into the residual stream: out[t, :] += tanh(alpha v) w + b with v the token's sum.
+__global__ void moe_combine_tanh_kernel(const float* __restrict__ y, long long ldy, const int* __restrict__ slot_of,
+                                        const float* __restrict__ weight_of, int top, int width,
+                                        const float* __restrict__ w, const float* __restrict__ b,
+                                        const float* __restrict__ alpha, float* __restrict__ out, long long ldo) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float a = alpha[0];
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float v = 0.0f;
+        for (int k = 0; k < top; ++k)
+            v += weight_of[(long long)t * top + k] * y[(long long)slot_of[(long long)t * top + k] * ldy + d];
+        out[(long long)t * ldo + d] += tanhf(a * v) * w[d] + (b ? b[d] : 0.0f);
+    }
+}
+
 }  // namespace mu
+
+MU_EXPORT int mu_moe_combine_tanh(const float* y, long long ldy, const int* slot_of, const float* weight_of, int n_tokens,
+                                  int top, int width, const float* w, const float* b, const float* alpha, float* out,
+                                  long long ldo, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!y || !slot_of || !weight_of || !out || !w || !alpha || top <= 0 || width <= 0) return MU_ERR_BAD_ARGUMENT;
+    return mu::launch_pdl(mu::moe_combine_tanh_kernel, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0,
+                          (cudaStream_t)stream, 1, y, ldy, slot_of, weight_of, top, width, w, b, alpha, out, ldo);
+}
 
 MU_EXPORT int mu_moe_tile_rows() { return mu::MOE_TM; }
 

@@ -41,7 +41,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const in
                     const __nv_bfloat16* __restrict__ w1, const __nv_bfloat16* __restrict__ w2, long long expert_stride,
                     long long ldw, const int* __restrict__ tile_info, const int* __restrict__ n_tiles, int n, int k,
                     TO* __restrict__ out, long long ldo, int n_rows, long long x_group_offset,
-                    long long out_group_offset) {
+                    long long out_group_offset, const __nv_bfloat16* __restrict__ gate, long long ldg) {
     extern __shared__ __align__(16) unsigned char mm_raw[];
     constexpr int MM_ROWS = 32 * WM, NW = 2 * WM;                               // rows a block; 8-column tiles a warp
     constexpr int STAGE = (MM_ROWS + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH;      // elements per stage
@@ -60,6 +60,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const in
     }
     x += (long long)e * x_group_offset;
     out += (long long)e * out_group_offset;
+    if (gate) gate += (long long)e * out_group_offset;          // the gate lies as the output does
     const int n0 = blockIdx.y * MM_COLS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid < MM_ROWS) {
@@ -151,6 +152,11 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const in
                     v0 = v0 / (1.0f + expf(-v0)) * acc2[m][j][2 * half];
                     v1 = v1 / (1.0f + expf(-v1)) * acc2[m][j][2 * half + 1];
                 }
+                if (gate) {                                      // out *= sigmoid(gate), in float32
+                    const __nv_bfloat16* gp = gate + (long long)(slot0 + r) * ldg + col;
+                    v0 = v0 / (1.0f + expf(-__bfloat162float(gp[0])));
+                    if (col + 1 < n) v1 = v1 / (1.0f + expf(-__bfloat162float(gp[1])));
+                }
                 TO* dst = out + (long long)(slot0 + r) * ldo + col;
                 dst[0] = from_float<TO>(v0);
                 if (col + 1 < n) dst[1] = from_float<TO>(v1);
@@ -161,7 +167,8 @@ template <typename TO, bool GATED, int WM>
 int launch_moe_mma(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, long long ldx, const int* pair_of, int top,
                    const __nv_bfloat16* w1, const __nv_bfloat16* w2, long long expert_stride, long long ldw,
                    const int* tile_info, const int* n_tiles, int n, int k, TO* out, long long ldo, int n_rows = 0,
-                   long long x_group_offset = 0, long long out_group_offset = 0) {
+                   long long x_group_offset = 0, long long out_group_offset = 0, const __nv_bfloat16* gate = nullptr,
+                   long long ldg = 0) {
     constexpr size_t smem = 2 * (32 * WM + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH * sizeof(__nv_bfloat16);
     static bool set = false;
     if (!set) {
@@ -171,7 +178,8 @@ int launch_moe_mma(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, long long 
         set = true;
     }
     return launch_pdl(moe_gemm_mma_kernel<TO, GATED, WM>, grid, dim3(MM_THREADS), smem, s, 1, x, ldx, pair_of, top, w1, w2,
-                      expert_stride, ldw, tile_info, n_tiles, n, k, out, ldo, n_rows, x_group_offset, out_group_offset);
+                      expert_stride, ldw, tile_info, n_tiles, n, k, out, ldo, n_rows, x_group_offset, out_group_offset, gate,
+                      ldg);
 }
 
 }  // namespace mu
@@ -208,10 +216,12 @@ MU_EXPORT int mu_moe_gemm_mma(const void* x, long long ldx, const int* pair_of, 
 // out[t, g, :] = W[g] x[t, g, :] for n_rows rows t and n_groups groups g (heads): x [n_rows][ldx] with group g's k
 // inputs at column g * x_group_offset; w [n_groups][n][k] (row stride ldw, group stride w_group_stride); out
 // [n_rows][ldo] with group g's n outputs at column g * out_group_offset.  bfloat16 operands, rows and slices
-// starting on 16-byte boundaries; out bfloat16 or float32.
+// starting on 16-byte boundaries; out bfloat16 or float32.  gate (bfloat16, laid out as out, row stride ldg; may be
+// null): out *= sigmoid(gate).
 MU_EXPORT int mu_heads_gemm(const void* x, long long ldx, long long x_group_offset, const void* w,
                             long long w_group_stride, long long ldw, int n_rows, int n_groups, int n, int k, void* out,
-                            long long ldo, long long out_group_offset, int out_bf16, void* stream) {
+                            long long ldo, long long out_group_offset, int out_bf16, const void* gate, long long ldg,
+                            void* stream) {
     if (n_rows <= 0 || n_groups <= 0) return MU_OK;
     if (!x || !w || !out || n <= 0 || k <= 0 || n_groups > 65535) return MU_ERR_BAD_ARGUMENT;
     if (k % 8 || ldx % 8 || ldw % 8 || w_group_stride % 8 || x_group_offset % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
@@ -223,7 +233,7 @@ MU_EXPORT int mu_heads_gemm(const void* x, long long ldx, long long x_group_offs
 #define MU_HG(TO, WM)                                                                                                  \
     return mu::launch_moe_mma<TO, false, WM>(grid, s, (const bf*)x, ldx, nullptr, 1, (const bf*)w, nullptr,             \
                                              w_group_stride, ldw, nullptr, nullptr, n, k, (TO*)out, ldo, n_rows,       \
-                                             x_group_offset, out_group_offset)
+                                             x_group_offset, out_group_offset, (const bf*)gate, ldg)
     if (out_bf16) {
         if (tile_rows == 64) MU_HG(bf, 2);
         MU_HG(bf, 1);

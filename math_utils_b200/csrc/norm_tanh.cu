@@ -21,7 +21,7 @@ __global__ void dynamic_tanh_kernel(const float* __restrict__ x, long long ldx, 
     const float a = alpha[0];
     const float* src = x + (rows ? (long long)rows[r] : (long long)r) * ldx;
     TO* dst = y + (long long)r * ldy;
-    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+    for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < hidden; d += gridDim.y * blockDim.x) {
         float v = tanhf(a * src[d]) * w[d] + (b ? b[d] : 0.0f);
         if (ADD) v += to_float(dst[d]);
         dst[d] = from_float<TO>(v);
@@ -71,7 +71,10 @@ MU_EXPORT int mu_dynamic_tanh(const float* x, long long ldx, const int* rows, co
     if (n_rows <= 0) return MU_OK;
     if (hidden <= 0 || !x || !w || !alpha || !y || (add && out_bf16)) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_rows), block(hidden >= 1024 ? 256 : 128);
+    // few rows (single-token steps): several blocks share a row, so that the tanh of a row is spread over the SMs
+    const int threads = hidden >= 1024 ? 256 : 128;
+    const int per_row = n_rows >= 256 ? 1 : (hidden + 2 * threads - 1) / (2 * threads);
+    const dim3 grid(n_rows, per_row > 0 ? per_row : 1), block(threads);
     if (out_bf16)
         return mu::launch_pdl(mu::dynamic_tanh_kernel<__nv_bfloat16, false>, grid, block, 0, s, 1, x, ldx, rows, w, b,
                               alpha, (__nv_bfloat16*)y, ldy, hidden);

@@ -89,7 +89,8 @@ _SIGNATURES = {
     "mu_rotary": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_f, _c_int, _c_int, _c_int,
                   _c_int, _c_p],
     "mu_latent_append": [_c_p, _c_ll, _c_p, _c_f, _c_p, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int,
-                         _c_int, _c_p, _c_int, _c_p],
+                         _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_p],
+    "mu_moe_combine_tanh": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p],
     "mu_latent_attention": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int,
                             _c_p, _c_ll, _c_p, _c_p, _c_int, _c_p],
     "mu_latent_merge": [_c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p],
@@ -104,7 +105,7 @@ _SIGNATURES = {
     "mu_moe_gemm_mma": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p,
                         _c_ll, _c_int, _c_p],
     "mu_heads_gemm": [_c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_ll, _c_int,
-                      _c_p],
+                      _c_p, _c_ll, _c_p],
     "mu_moe_combine": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_p],
     "mu_moe_tile_rows": [],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int,
@@ -335,22 +336,40 @@ def rotary(x: torch.Tensor, out: torch.Tensor, tok_pos: torch.Tensor, freqs: tor
     return out
 
 
-def latent_append(dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, freqs: torch.Tensor, magnitude: float,
-                  rot_dims: int, kv_rank: int, rot_dim: int, tok_pos, tok_seq, block_table: torch.Tensor,
-                  page_tokens: int, rows: torch.Tensor) -> None:
+def latent_append(dkv: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float, freqs: torch.Tensor,
+                  magnitude: float, rot_dims: int, kv_rank: int, rot_dim: int, tok_pos, tok_seq,
+                  block_table: torch.Tensor, page_tokens: int, rows: torch.Tensor, queries=None) -> None:
     """Per token: the RMS norm of the first ``kv_rank`` values of ``dkv`` and the rotation of the last ``rot_dim``
-    go to the token's row of the latent cache ``rows`` [pages, page_tokens, kv_rank + rot_dim]."""
+    go to the token's row of the latent cache ``rows`` [pages, page_tokens, kv_rank + rot_dim].
+
+    ``queries`` = (q, q_head_stride, qa, qa_head_stride, n_heads): the same launch rotates every head's ``rot_dim``
+    entries (views whose first element is head 0's first rotated entry) from ``q`` into the float32 ``qa``.  With
+    ``dkv`` None only that is done (a layer that reads another layer's cache)."""
     _need_cuda(dkv, norm_weight, freqs, tok_pos, tok_seq, block_table, rows)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
-    if dkv.dtype != rows.dtype or dkv.stride(1) != 1 or dkv.shape[1] != kv_rank + rot_dim or not rows.is_contiguous():
-        raise KernelError("latent_append: the projection and the cache must share a dtype and the row width")
-    if rows.shape[1] != page_tokens or rows.shape[2] != kv_rank + rot_dim:
-        raise KernelError("latent_append: the cache is not [pages, page_tokens, kv_rank + rot_dim]")
-    _check(library().mu_latent_append(_ptr(dkv), dkv.stride(0), _ptr(norm_weight), float(eps), _ptr(freqs),
-                                      float(magnitude), int(rot_dims), int(kv_rank), int(rot_dim), _ptr(tok_pos),
-                                      _ptr(tok_seq), _ptr(block_table), block_table.shape[1], int(page_tokens),
-                                      dkv.shape[0], _ptr(rows), _is_bf16(rows), _stream()), "latent_append")
+    if dkv is not None:
+        if dkv.dtype != rows.dtype or dkv.stride(1) != 1 or dkv.shape[1] != kv_rank + rot_dim or not rows.is_contiguous():
+            raise KernelError("latent_append: the projection and the cache must share a dtype and the row width")
+        if rows.shape[1] != page_tokens or rows.shape[2] != kv_rank + rot_dim:
+            raise KernelError("latent_append: the cache is not [pages, page_tokens, kv_rank + rot_dim]")
+    q = qa = None
+    qs = qas = heads = 0
+    if queries is not None:
+        q, qs, qa, qas, heads = queries
+        _need_cuda(q, qa)
+        if q.dtype != rows.dtype or qa.dtype != torch.float32 or q.stride(1) != 1 or qa.stride(1) != 1:
+            raise KernelError("latent_append: queries in the cache's dtype, rotated queries as float32")
+    elif dkv is None:
+        raise KernelError("latent_append: nothing to do")
+    n_tokens = dkv.shape[0] if dkv is not None else q.shape[0]
+    _check(library().mu_latent_append(_ptr(dkv), dkv.stride(0) if dkv is not None else 0, _ptr(norm_weight), float(eps),
+                                      _ptr(freqs), float(magnitude), int(rot_dims), int(kv_rank), int(rot_dim),
+                                      _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), block_table.shape[1],
+                                      int(page_tokens), n_tokens, _ptr(rows), _is_bf16(rows), _ptr(q),
+                                      q.stride(0) if q is not None else 0, int(qs), _ptr(qa),
+                                      qa.stride(0) if qa is not None else 0, int(qas), int(heads), _stream()),
+           "latent_append")
 
 
 def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Tensor, page_tokens: int, tok_pos, tok_seq,
@@ -476,22 +495,30 @@ def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: tor
     return out
 
 
-def heads_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: int, out_head_stride: int) -> torch.Tensor:
+def heads_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: int, out_head_stride: int,
+               gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, h, :] = W[h] x[t, h, :] for every row t and head h: ``w`` [heads, n, k]; ``x`` / ``out`` views whose first
     element is head 0's first entry, a head's slice ``x_head_stride`` / ``out_head_stride`` elements after the head
     before.  bfloat16 operands with aligned slices run as ONE launch on the tensor cores; anything else head by head
-    through ``linear``."""
-    _need_cuda(x, w, out)
+    through ``linear``.  ``gate`` (laid out as ``out``): out *= sigmoid(gate), in the product's epilogue where that
+    launch runs, as a launch of its own otherwise."""
+    _need_cuda(x, w, out, gate)
     heads, n, k = w.shape
     if (LATENT_TC and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and k % 8 == 0
             and x.stride(0) % 8 == 0 and x_head_stride % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and x.stride(1) == 1 and out.stride(1) == 1):
+        fused = gate is not None and gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape == out.shape
         _check(library().mu_heads_gemm(_ptr(x), x.stride(0), int(x_head_stride), _ptr(w), w.stride(0), w.stride(1),
                                        x.shape[0], heads, n, k, _ptr(out), out.stride(0), int(out_head_stride),
-                                       _is_bf16(out), _stream()), ("heads_gemm(heads={}, n={}, k={})", heads, n, k))
+                                       _is_bf16(out), _ptr(gate) if fused else None, gate.stride(0) if fused else 0,
+                                       _stream()), ("heads_gemm(heads={}, n={}, k={})", heads, n, k))
+        if gate is not None and not fused:
+            sigmoid_gate(out, gate)
         return out
     for h in range(heads):
         linear(x[:, h * x_head_stride: h * x_head_stride + k], w[h], out=out[:, h * out_head_stride: h * out_head_stride + n])
+    if gate is not None:
+        sigmoid_gate(out, gate)
     return out
 
 
@@ -502,6 +529,19 @@ def moe_combine(y: torch.Tensor, slot_of: torch.Tensor, weight_of: torch.Tensor,
         raise KernelError("moe_combine works on float32 rows with unit inner stride")
     _check(library().mu_moe_combine(_ptr(y), y.stride(0), _ptr(slot_of), _ptr(weight_of), out.shape[0], int(top),
                                     out.shape[1], _ptr(out), out.stride(0), _stream()), "moe_combine")
+    return out
+
+
+def moe_combine_tanh(y: torch.Tensor, slot_of: torch.Tensor, weight_of: torch.Tensor, top: int, weight: torch.Tensor,
+                     bias: Optional[torch.Tensor], alpha: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] += tanh(alpha v) * weight + bias with v = the token's weighted sum of its experts' rows (``moe_combine``
+    and ``dynamic_tanh(add=True)`` in one launch)."""
+    _need_cuda(y, slot_of, weight_of, weight, bias, alpha, out)
+    if y.dtype != torch.float32 or out.dtype != torch.float32 or y.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("moe_combine_tanh works on float32 rows with unit inner stride")
+    _check(library().mu_moe_combine_tanh(_ptr(y), y.stride(0), _ptr(slot_of), _ptr(weight_of), out.shape[0], int(top),
+                                         out.shape[1], _ptr(weight), _ptr(bias), _ptr(alpha), _ptr(out), out.stride(0),
+                                         _stream()), "moe_combine_tanh")
     return out
 
 

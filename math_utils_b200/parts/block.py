@@ -117,8 +117,11 @@ class SandwichNormBlock(Arrangement):
         if not isinstance(layer.feed_forward, NoFeedForward):
             h = layer.norm2.forward(x)
             ctx.note("ln2", h)
-            self._sublayer(layer.feed_forward, y, h, y, ctx)
-            layer.extra["norm2b"].add_into(y, x)
+            if getattr(layer.feed_forward, "fuses_output_norm", False):
+                layer.feed_forward.forward(h, x, ctx, output_norm=layer.extra["norm2b"])
+            else:
+                self._sublayer(layer.feed_forward, y, h, y, ctx)
+                layer.extra["norm2b"].add_into(y, x)
         ctx.note("res2", x)
 
     @staticmethod

@@ -81,17 +81,17 @@ class LatentAttention(Mixer):
         self.proj(h, out=proj)
         ctx.note("proj", proj)
         table = ctx.block_tables[cache.group]
-        if owns_cache:
-            if not self.own_kv:
-                raise ConfigError("a latent-attention layer without a down-projection cannot own a cache")
-            ops.latent_append(views[3], self.norm_weight, self.eps, self.freq_table, self.magnitude, self.rot_dims,
-                              r, self.rot_dim, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens, cache.pages)
+        if owns_cache and not self.own_kv:
+            raise ConfigError("a latent-attention layer without a down-projection cannot own a cache")
         # queries in latent space, float32: [T, H, kv_rank | rot_dim]
         qa = ctx.buffer("latent.q", (T, H * self.row), torch.float32)
+        # one launch: this step's cache rows (norm, rotation) and the rotated part of the queries
+        rotated = (q[:, self.dim:], self.q_head, qa[:, r:], self.row, H) if self.rot_dim else None
+        if owns_cache or rotated is not None:
+            ops.latent_append(views[3] if owns_cache else None, self.norm_weight, self.eps, self.freq_table,
+                              self.magnitude, self.rot_dims, r, self.rot_dim, ctx.tok_pos, ctx.tok_seq, table,
+                              cache.page_tokens, cache.pages, queries=rotated)
         ops.heads_gemm(q, self.q_up, qa, self.q_head, self.row)
-        if self.rot_dim:
-            ops.rotary(q[:, self.dim:], qa[:, r:], ctx.tok_pos, self.freq_table, self.magnitude, H, self.rot_dims,
-                       self.rot_dim, self.q_head, self.row)
         ctx.note("q_latent", qa)
         mixed = ctx.buffer("latent.mixed", (T, H * r), dt)
         n_splits, part_o, part_ml = self.splits(ctx)
@@ -99,8 +99,7 @@ class LatentAttention(Mixer):
                              mixed, n_splits, part_o, part_ml, tiles=ctx.q_tiles, single_tokens=ctx.is_decode)
         ctx.note("mixed", mixed)
         heads = ctx.buffer("latent.heads", (T, H * self.vdim), dt)
-        ops.heads_gemm(mixed, self.v_up, heads, r, self.vdim)
-        ops.sigmoid_gate(heads, gate)
+        ops.heads_gemm(mixed, self.v_up, heads, r, self.vdim, gate=gate)
         ctx.note("attn", heads)
         self.out(heads, residual=residual if accumulate else None, out=residual)
 

@@ -54,7 +54,9 @@ class RoutedExperts(FeedForward):
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
         self.tile_rows = runtime.ops.moe_tile_rows()
 
-    def forward(self, h, residual, ctx, accumulate: bool = True) -> None:
+    fuses_output_norm = True           # forward(..., output_norm=): the norm of the result, added into the stream
+
+    def forward(self, h, residual, ctx, accumulate: bool = True, output_norm=None) -> None:
         ops, dt = self.runtime.ops, self.runtime.dtype
         T, top, E = ctx.n_tokens, self.top, self.n_experts
         P = T * top
@@ -76,7 +78,17 @@ class RoutedExperts(FeedForward):
         ctx.note("act", hidden)
         y = ctx.buffer("moe.out", (P, self.hidden_size), torch.float32)
         ops.moe_gemm(hidden, None, top, self.w_down, None, tile_info, n_tiles, max_tiles, y, tile_rows=tile_rows)
-        if accumulate:
+        if output_norm is not None:
+            # residual += norm(sum of the token's experts); Dynamic Tanh in the same launch as the sum
+            from .norm import DynamicTanh
+            if type(output_norm) is DynamicTanh:
+                ops.moe_combine_tanh(y, slot_of, weight_of, top, output_norm.weight, output_norm.bias, output_norm.alpha,
+                                     residual)
+            else:
+                mixed = ctx.buffer("moe.mixed", (T, self.hidden_size), torch.float32)
+                ops.moe_combine(y, slot_of, weight_of, top, mixed)
+                output_norm.add_into(mixed, residual)
+        elif accumulate:
             mixed = ctx.buffer("moe.mixed", (T, self.hidden_size), torch.float32)
             ops.moe_combine(y, slot_of, weight_of, top, mixed)
             residual += mixed

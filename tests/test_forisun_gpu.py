@@ -395,6 +395,17 @@ def test_latent_append_kernel(dtype):
         row = got[table[s, p // 64], p % 64]
         assert np.abs(row - want[t]).max() < (1e-5 if dtype == torch.float32 else 3e-2)
     assert np.count_nonzero(got.reshape(-1, kv_rank + rot_dim).any(axis=1)) == 5      # no other row was touched
+    # the same launch rotates the queries' rotated parts; and alone, for a layer that borrows its cache
+    heads, lead = 3, 7
+    q = dev(rng.normal(0, 1, (5, heads * (lead + rot_dim))), dtype)
+    want_q = plain.rotate(q.float().cpu().numpy().astype(np.float64).reshape(5, heads, lead + rot_dim)[..., lead:], positions, rot)
+    for with_rows in (True, False):
+        qa = torch.zeros((5, heads * (2 + rot_dim)), device="cuda")
+        ops.latent_append(dkv if with_rows else None, dev(w), eps, dev(np.array(freqs)), mag, dims, kv_rank, rot_dim,
+                          dev(positions, torch.int32), dev(seq_of, torch.int32), dev(table, torch.int32), 64, pages,
+                          queries=(q[:, lead:], lead + rot_dim, qa[:, 2:], 2 + rot_dim, heads))
+        got_q = qa.cpu().numpy().reshape(5, heads, 2 + rot_dim)
+        assert np.abs(got_q[..., 2:] - want_q).max() < 1e-5 and not got_q[..., :2].any()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -436,6 +447,12 @@ def test_routed_experts_kernels(dtype, experts, top, tokens, D, F, tc):
     out = torch.zeros((tokens, D), device="cuda")
     ops.moe_combine(y, slot_of, weight_of, top, out)
     assert np.abs(out.cpu().numpy() - want).max() < (3e-5 if dtype == torch.float32 else 3e-2) * max(1.0, np.abs(want).max())
+    # the sum, Dynamic Tanh and the addition to the stream in one launch
+    nw, nb, stream = rng.normal(1, 0.2, D), rng.normal(0, 0.2, D), rng.normal(0, 1, (tokens, D))
+    acc = dev(stream)
+    ops.moe_combine_tanh(y, slot_of, weight_of, top, dev(nw), dev(nb), dev(np.array([0.7])), acc)
+    want2 = acc.cpu().numpy() * 0 + dev(stream).cpu().numpy() + plain.dynamic_tanh(out.cpu().numpy().astype(np.float64), nw, nb, 0.7)
+    assert np.abs(acc.cpu().numpy() - want2).max() < 1e-5
 
 
 def test_sigmoid_gate_kernel():
@@ -463,3 +480,11 @@ def test_products_per_head(dtype, out_dtype, rows, heads, n, k, lead):
         want = xf[:, h * xs: h * xs + k] @ wf[h].T
         assert np.abs(got[:, h, :n] - want).max() < (2e-5 if out_dtype == torch.float32 else 3e-2)
         assert not got[:, h, n:].any()                                      # nothing written between the slices
+    if out_dtype == dtype:                                                  # with a gate laid out as the output
+        gate = dev(rng.normal(0, 2, (rows, heads * os_)), dtype)
+        ops.heads_gemm(x, w, out, xs, os_, gate=gate)
+        got = out.float().cpu().numpy().reshape(rows, heads, os_)
+        gf = gate.float().cpu().numpy().astype(np.float64).reshape(rows, heads, os_)
+        for h in range(heads):
+            want = xf[:, h * xs: h * xs + k] @ wf[h].T * plain.sigmoid(gf[:, h, :n])
+            assert np.abs(got[:, h, :n] - want).max() < (2e-5 if out_dtype == torch.float32 else 3e-2)
