@@ -264,7 +264,7 @@ int latent_attention_any(const float* q, const T* rows, const int* block_table, 
     if (width <= 32 * N)                                                                                              \
         return launch_latent_attention<T, N>(q, rows, block_table, max_pages, page_tokens, tok_pos, tok_seq, n_tokens, \
                                              n_heads, kv_rank, width, scale, n_splits, out, ldo, part_o, part_ml, s);
-    MU_LA(2) MU_LA(4) MU_LA(6) MU_LA(8) MU_LA(12) MU_LA(16) MU_LA(20) MU_LA(24)
+    MU_LA(2) MU_LA(4) MU_LA(6) MU_LA(8) MU_LA(12) MU_LA(16) MU_LA(20) MU_LA(24) MU_LA(32) MU_LA(48)
 #undef MU_LA
     return MU_ERR_UNSUPPORTED_SIZE;
 }
