@@ -15,7 +15,14 @@
 
 namespace mu {
 
-constexpr int MM_COLS = 128, MM_K = 64, MM_PITCH = MM_K + 8, MM_THREADS = 256;
+constexpr int MM_COLS = 128, MM_THREADS = 256;
+#ifndef MU_MM_K
+#define MU_MM_K 64
+#endif
+#ifndef MU_MM_STAGES
+#define MU_MM_STAGES 2
+#endif
+constexpr int MM_K = MU_MM_K, MM_STAGES = MU_MM_STAGES, MM_PITCH = MM_K + 8;
 
 __device__ __forceinline__ void mm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -75,39 +82,41 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const in
         __nv_bfloat16* sa = sm + stage * STAGE;
         __nv_bfloat16* sb1 = sa + MM_ROWS * MM_PITCH;
         __nv_bfloat16* sb2 = sb1 + MM_COLS * MM_PITCH;
+        constexpr int CPR = MM_K / 8;                            // 16-byte pieces a row
 #pragma unroll
-        for (int i = 0; i < WM; ++i) {
-            const int r = (tid >> 3) + 32 * i, c = (tid & 7) * 8;
+        for (int idx = tid; idx < MM_ROWS * CPR; idx += MM_THREADS) {
+            const int r = idx / CPR, c = (idx % CPR) * 8;
             const int left = (k - (k0 + c)) * 2;
             const int bytes = left >= 16 ? 16 : (left > 0 ? left : 0);
             mm_cp_async16(sa + r * MM_PITCH + c, x + (long long)src_row[r] * ldx + (bytes ? k0 + c : 0), bytes);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int idx = tid + i * MM_THREADS;
-            const int r = idx >> 3, c = (idx & 7) * 8;
+        for (int idx = tid; idx < MM_COLS * CPR; idx += MM_THREADS) {
+            const int r = idx / CPR, c = (idx % CPR) * 8;
             const int left = (k - (k0 + c)) * 2;
             const int bytes = left >= 16 ? 16 : (left > 0 ? left : 0);
             const long long row = min(n0 + r, n - 1);            // columns past n repeat the last one
             mm_cp_async16(sb1 + r * MM_PITCH + c, w1e + row * ldw + (bytes ? k0 + c : 0), bytes);
             if (GATED) mm_cp_async16(sb2 + r * MM_PITCH + c, w2e + row * ldw + (bytes ? k0 + c : 0), bytes);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     float acc1[2][NW][4] = {}, acc2[GATED ? 2 : 1][NW][4] = {};
     const int row_base = WM == 2 ? (warp >> 2) * 32 : 0, col_base = WM == 2 ? (warp & 3) * 32 : warp * 16;
     const int chunks = (k + MM_K - 1) / MM_K;
-    load(0, 0);
+    // a ring of MM_STAGES stages: MM_STAGES - 1 chunks on their way while one is worked on; a group is committed
+    // for every chunk index, empty past the end, so that the wait below always counts the same
+#pragma unroll
+    for (int i = 0; i < MM_STAGES - 1; ++i) {
+        if (i < chunks) load(i * MM_K, i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     for (int ch = 0; ch < chunks; ++ch) {
-        const int stage = ch & 1;
-        if (ch + 1 < chunks) {
-            load((ch + 1) * MM_K, stage ^ 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncthreads();
+        const int stage = ch % MM_STAGES;
+        asm volatile("cp.async.wait_group %0;" :: "n"(MM_STAGES - 2) : "memory");
+        __syncthreads();                                         // chunk ch has landed; everyone is done with chunk ch - 1
+        if (ch + MM_STAGES - 1 < chunks) load((ch + MM_STAGES - 1) * MM_K, (ch + MM_STAGES - 1) % MM_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
         const __nv_bfloat16* sa = sm + stage * STAGE;
         const __nv_bfloat16* sb1 = sa + MM_ROWS * MM_PITCH;
         const __nv_bfloat16* sb2 = sb1 + MM_COLS * MM_PITCH;
@@ -135,7 +144,6 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const in
                 }
             }
         }
-        __syncthreads();
     }
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
@@ -169,7 +177,7 @@ int launch_moe_mma(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, long long 
                    const int* tile_info, const int* n_tiles, int n, int k, TO* out, long long ldo, int n_rows = 0,
                    long long x_group_offset = 0, long long out_group_offset = 0, const __nv_bfloat16* gate = nullptr,
                    long long ldg = 0) {
-    constexpr size_t smem = 2 * (32 * WM + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH * sizeof(__nv_bfloat16);
+    constexpr size_t smem = MM_STAGES * (32 * WM + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH * sizeof(__nv_bfloat16);
     static bool set = false;
     if (!set) {
         if (cudaFuncSetAttribute(moe_gemm_mma_kernel<TO, GATED, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
