@@ -88,10 +88,15 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
         row_src[tid] = valid ? (first + i) * n_heads + head0 + h : -1;
     }
     __syncthreads();
-    for (int idx = tid; idx < LM_ROWS * width; idx += LM_THREADS) {
-        const int r = idx / width, d = idx % width;
+    // the queries, rounded to bfloat16: a warp a row, lanes along it in pairs (no division; width is even)
+    for (int r = warp; r < LM_ROWS; r += LM_THREADS / 32) {
         const int src = row_src[r];
-        Qs[r * w8 + d] = __float2bfloat16_rn(src >= 0 ? q[(long long)src * width + d] : 0.0f);
+        const float2* from = reinterpret_cast<const float2*>(q + (long long)(src >= 0 ? src : 0) * width);
+        __nv_bfloat162* to = reinterpret_cast<__nv_bfloat162*>(Qs + r * w8);
+        for (int d = lane; d < width / 2; d += 32) {
+            const float2 v = src >= 0 ? from[d] : make_float2(0.0f, 0.0f);
+            to[d] = __floats2bfloat162_rn(v.x, v.y);
+        }
     }
     const int n_keys = pos0 + count;
     const int n_pages = (n_keys + LM_KEYS - 1) / LM_KEYS;
