@@ -19,6 +19,13 @@ Layers are grouped by what their mixer keeps (its ``cache_spec``):
     gets the same kind of group with pages of ``[page_tokens, width]``.
   * a ``StateGroup`` for each distinct state size: ``[n_slots, n_values]``
     float32 per cache entry, zeroed when a slot is taken.
+A mixer made of several mixers side by side (``CompositeCacheSpec``) gets a view per
+member, each member's storage in the group of its own kind.
+
+Beside the groups the cache keeps one int32 per slot on the device, ``last_tokens``:
+the last token a slot's sequence was fed, for an embedding that looks at the token
+before (the embedding's kernel reads and writes it; position 0 never reads it, so a
+slot that is taken again needs no reset).
 
 Bookkeeping is host-side and plain Python; storage is torch tensors on the
 device given (a CUDA device in the engine, the CPU in bookkeeping tests).
@@ -31,7 +38,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.base import KVCacheSpec, RowCacheSpec, StateCacheSpec
+from ..parts.base import CompositeCacheSpec, KVCacheSpec, RowCacheSpec, StateCacheSpec
 
 PAGE_TOKENS = 64
 
@@ -212,9 +219,18 @@ class SequenceCache:
         self.kv_groups: List[KVGroup] = []
         self.state_groups: List[StateGroup] = []
         self._entry_view: Dict[int, object] = {}
-        by_spec: Dict[object, List[int]] = {}
+        self.last_tokens = torch.zeros(self.n_slots, dtype=torch.int32, device=device)
+        self.keeps_last_token = False          # set by the model whose embedding reads last_tokens
+        by_spec: Dict[object, List[object]] = {}
+        composite: Dict[int, List[object]] = {}
         for i, spec in enumerate(entry_specs):
-            if spec is not None:
+            if isinstance(spec, CompositeCacheSpec):
+                # a member's storage is keyed (entry, member) in the group of its own kind
+                composite[i] = [None if m is None else (i, j) for j, m in enumerate(spec.members)]
+                for j, m in enumerate(spec.members):
+                    if m is not None:
+                        by_spec.setdefault(m, []).append((i, j))
+            elif spec is not None:
                 by_spec.setdefault(spec, []).append(i)
         for spec, entries in by_spec.items():
             if isinstance(spec, (KVCacheSpec, RowCacheSpec)):
@@ -230,6 +246,8 @@ class SequenceCache:
                     self._entry_view[e] = StateEntryView(g.storage[e], spec)
             else:
                 raise CacheError(f"schedule entry {entries[0]}: unknown cache spec {spec!r}")
+        for i, keys in composite.items():
+            self._entry_view[i] = tuple(None if k is None else self._entry_view.pop(k) for k in keys)
 
     # ------------------------------------------------------------------ slots
     def acquire(self) -> int:
@@ -293,9 +311,28 @@ class SequenceCache:
         self._check(slot)
         if not 0 <= length <= int(self.lengths[slot]):
             raise CacheError(f"slot {slot} holds {int(self.lengths[slot])} positions, cannot cut it to {length}")
-        if length < int(self.lengths[slot]) and (self.state_groups or any(g.spec.window > 0 for g in self.kv_groups)):
+        if length < int(self.lengths[slot]) and (self.has_running_state or any(g.spec.window > 0 for g in self.kv_groups)):
             raise CacheError("a cache with a windowed group or with fixed-size state cannot be cut back")
         self.lengths[slot] = length
+
+    @property
+    def has_running_state(self) -> bool:
+        """Whether a slot holds anything that a step moves on for good (fixed-size state, the last token)."""
+        return bool(self.state_groups) or self.keeps_last_token
+
+    def snapshot_state(self, slots: Sequence[int]):
+        """A copy of everything the given slots hold that a step moves on for good; ``restore_state`` puts it
+        back (a step that ran only to set kernels up, before the same step is recorded and replayed)."""
+        index = torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
+        return (index, [[t[index].clone() for t in g.storage.values()] for g in self.state_groups],
+                self.last_tokens[index].clone())
+
+    def restore_state(self, snapshot) -> None:
+        index, groups, last = snapshot
+        for g, kept in zip(self.state_groups, groups):
+            for t, rows in zip(g.storage.values(), kept):
+                t[index] = rows
+        self.last_tokens[index] = last
 
     def entry(self, index: int):
         """The view of schedule entry ``index``'s cache, or None if it owns none."""

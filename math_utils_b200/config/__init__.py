@@ -3,6 +3,7 @@ from .base import (ConfigError, KeyReader, LayerSpec, ModelPlan, PartSpec,
                    ScheduleEntry, default_schedule)
 from .forisun import ForisunConfig
 from .gpt2 import Gpt2Config
+from .lusalorn import LusalornConfig
 from .registry import (Architecture, architecture_for, known_architectures,
                        load_config, read_config_json, register_architecture)
 
@@ -14,9 +15,10 @@ register_architecture(Architecture(
 ), replace=True)
 
 register_architecture(Architecture(names=("Forisun", "forisun"), config_class=ForisunConfig), replace=True)
+register_architecture(Architecture(names=("Lusalorn", "lusalorn"), config_class=LusalornConfig), replace=True)
 
 __all__ = [
-    "Architecture", "ConfigError", "ForisunConfig", "Gpt2Config", "KeyReader", "LayerSpec", "ModelPlan",
+    "Architecture", "ConfigError", "ForisunConfig", "Gpt2Config", "KeyReader", "LayerSpec", "LusalornConfig", "ModelPlan",
     "PartSpec", "ScheduleEntry", "architecture_for", "default_schedule",
     "known_architectures", "load_config", "read_config_json", "register_architecture",
 ]

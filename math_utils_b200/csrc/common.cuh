@@ -32,6 +32,7 @@ namespace mu {
 constexpr int ACT_NONE = 0;
 constexpr int ACT_GELU_NEW = 1;   // tanh form
 constexpr int ACT_GELU_ERF = 2;   // exact form
+constexpr int ACT_SILU = 3;       // z * sigmoid(z): for the gated feed-forward's own kernel
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

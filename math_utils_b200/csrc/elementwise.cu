@@ -28,6 +28,47 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     }
 }
 
+// x[t, :] = table[id[t], :] + pair_table[row, :] with row = (previous token * mul_prev + id[t] * mul_cur) mod buckets,
+// and row = buckets (the table's last row) for the first token of a sequence.  The token before the step's
+// first token of a sequence is what last_token[slot] holds.  With `remember` (every sequence brings one token)
+// the block also stores its token there; for longer runs remember_tokens_kernel does, after this kernel.
+template <typename TW>
+__global__ void embed_pair_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const int* __restrict__ tok_seq,
+                                  const int* __restrict__ seq_slots, int* __restrict__ last_token,
+                                  const TW* __restrict__ table, const TW* __restrict__ pair_table, float* __restrict__ x,
+                                  int hidden, int buckets, long long mul_prev, long long mul_cur, int remember) {
+    __shared__ long long pair_row;
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const long long id = ids[t];
+    if (threadIdx.x == 0) {
+        long long row = buckets;
+        const int slot = seq_slots[tok_seq[t]];
+        if (pos[t] > 0) {
+            const long long prev = (t > 0 && tok_seq[t - 1] == tok_seq[t]) ? ids[t - 1] : last_token[slot];
+            row = (prev * mul_prev + id * mul_cur) % buckets;
+            if (row < 0) row += buckets;
+        }
+        pair_row = row;
+        if (remember) last_token[slot] = (int)id;
+    }
+    __syncthreads();
+    const TW* src = table + id * hidden;
+    const TW* psrc = pair_table + pair_row * hidden;
+    float* dst = x + (long long)t * hidden;
+#pragma unroll 4
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) dst[d] = to_float(src[d]) + to_float(psrc[d]);
+}
+
+__global__ void remember_tokens_kernel(const int* __restrict__ ids, const int* __restrict__ seq_first,
+                                       const int* __restrict__ seq_slots, int* __restrict__ last_token, int n_seqs) {
+    pdl_trigger();
+    pdl_wait();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < n_seqs && seq_first[s + 1] > seq_first[s]) last_token[seq_slots[s]] = ids[seq_first[s + 1] - 1];
+}
+
 // One block per output row.  The row is staged in shared memory so that the
 // mean, the variance and the output each read it once from there.
 template <typename TO>
@@ -154,6 +195,29 @@ MU_EXPORT int mu_embed(const int* ids, const int* pos, const void* table, const 
                               (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden, scale);
     return mu::launch_pdl(mu::embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
                           (const float*)table, (const float*)pos_table, x, hidden, scale);
+}
+
+// Token rows plus hashed rows of (token before, token); single_tokens: every sequence brings one token.
+MU_EXPORT int mu_embed_pair(const int* ids, const int* pos, const int* tok_seq, const int* seq_first, const int* seq_slots,
+                            int* last_token, const void* table, const void* pair_table, float* x, int n_tokens, int n_seqs,
+                            int hidden, int buckets, long long mul_prev, long long mul_cur, int table_bf16,
+                            int single_tokens, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (hidden <= 0 || buckets <= 0 || !ids || !pos || !tok_seq || !seq_first || !seq_slots || !last_token || !table ||
+        !pair_table || !x)
+        return MU_ERR_BAD_ARGUMENT;
+    const int threads = hidden >= 256 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int code =
+        table_bf16 ? mu::launch_pdl(mu::embed_pair_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
+                                    tok_seq, seq_slots, last_token, (const __nv_bfloat16*)table,
+                                    (const __nv_bfloat16*)pair_table, x, hidden, buckets, mul_prev, mul_cur, single_tokens)
+                   : mu::launch_pdl(mu::embed_pair_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos, tok_seq,
+                                    seq_slots, last_token, (const float*)table, (const float*)pair_table, x, hidden,
+                                    buckets, mul_prev, mul_cur, single_tokens);
+    if (code != MU_OK || single_tokens) return code;
+    return mu::launch_pdl(mu::remember_tokens_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, 1, ids, seq_first,
+                          seq_slots, last_token, n_seqs);
 }
 
 // rows: optional int32 row indices into x (n_rows of them); out_bf16 picks the output dtype.

@@ -1,0 +1,95 @@
+// Small element-by-element kernels around products.
+//
+// mu_gated_act    out[t][f] = act(a[t][f]) * a[t][F + f]: the two halves of one product's output (gate | up) of a
+//                 gated feed-forward; the activation in float32, storage in the compute dtype.
+// mu_scaled_sum   y (+)= a * p + b * q, float32: two branches that join with a weight each.
+// mu_cast_rows    float32 rows to bfloat16 rows.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace mu {
+
+__device__ __forceinline__ float gate_act(float z, int act) {
+    if (act == ACT_SILU) return z / (1.0f + expf(-z));
+    return apply_act(z, act);
+}
+
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ a, long long lda, T* __restrict__ out, long long ldo, int n_rows,
+                                 int width, int act) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)n_rows * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / width;
+        const int c = (int)(i % width);
+        const float g = to_float(a[r * lda + c]), u = to_float(a[r * lda + width + c]);
+        out[r * ldo + c] = from_float<T>(gate_act(g, act) * u);
+    }
+}
+
+template <bool ADD>
+__global__ void scaled_sum_kernel(const float* __restrict__ p, long long ldp, float a, const float* __restrict__ q,
+                                  long long ldq, float b, float* __restrict__ y, long long ldy, int n_rows, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)n_rows * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / width;
+        const int c = (int)(i % width);
+        float v = a * p[r * ldp + c] + b * q[r * ldq + c];
+        if (ADD) v += y[r * ldy + c];
+        y[r * ldy + c] = v;
+    }
+}
+
+__global__ void cast_rows_kernel(const float* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y, long long ldy,
+                                 int n_rows, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)n_rows * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / width;
+        const int c = (int)(i % width);
+        y[r * ldy + c] = __float2bfloat16_rn(x[r * ldx + c]);
+    }
+}
+
+inline unsigned blocks_for(long long total) {
+    const long long b = (total + 255) / 256;
+    return (unsigned)(b > 8192 ? 8192 : b);
+}
+
+}  // namespace mu
+
+MU_EXPORT int mu_gated_act(const void* a, long long lda, void* out, long long ldo, int n_rows, int width, int act,
+                           int is_bf16, void* stream) {
+    if (n_rows <= 0 || width <= 0) return MU_OK;
+    if (!a || !out || act < 0 || act > mu::ACT_SILU) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(mu::blocks_for((long long)n_rows * width)), block(256);
+    if (is_bf16)
+        return mu::launch_pdl(mu::gated_act_kernel<__nv_bfloat16>, grid, block, 0, s, 1, (const __nv_bfloat16*)a, lda,
+                              (__nv_bfloat16*)out, ldo, n_rows, width, act);
+    return mu::launch_pdl(mu::gated_act_kernel<float>, grid, block, 0, s, 1, (const float*)a, lda, (float*)out, ldo, n_rows,
+                          width, act);
+}
+
+MU_EXPORT int mu_scaled_sum(const float* p, long long ldp, float a, const float* q, long long ldq, float b, float* y,
+                            long long ldy, int n_rows, int width, int add, void* stream) {
+    if (n_rows <= 0 || width <= 0) return MU_OK;
+    if (!p || !q || !y) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(mu::blocks_for((long long)n_rows * width)), block(256);
+    if (add) return mu::launch_pdl(mu::scaled_sum_kernel<true>, grid, block, 0, s, 1, p, ldp, a, q, ldq, b, y, ldy, n_rows, width);
+    return mu::launch_pdl(mu::scaled_sum_kernel<false>, grid, block, 0, s, 1, p, ldp, a, q, ldq, b, y, ldy, n_rows, width);
+}
+
+MU_EXPORT int mu_cast_rows(const float* x, long long ldx, void* y, long long ldy, int n_rows, int width, void* stream) {
+    if (n_rows <= 0 || width <= 0) return MU_OK;
+    if (!x || !y) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(mu::blocks_for((long long)n_rows * width)), block(256);
+    return mu::launch_pdl(mu::cast_rows_kernel, grid, block, 0, s, 1, x, ldx, (__nv_bfloat16*)y, ldy, n_rows, width);
+}

@@ -1,0 +1,306 @@
+// Attention whose heads have one or two score maps, normed and rotated queries and keys, and values of
+// their own size, over a paged cache that keeps ONE row per position:
+//     row = [ keys: kv head 0 {map 0 | map 1}, kv head 1 {...}, ... | values: kv head 0, kv head 1, ... ]
+// (`maps` * dim entries per kv head of keys, vdim entries per kv head of values).  Pages hold `page_tokens`
+// rows; block_table[s][i] is the page with positions [i * page_tokens, (i + 1) * page_tokens) of the step's
+// s-th sequence.
+//
+// mu_qk_prepare        per token: every (head, map) slice of the queries and of the keys is brought to unit
+//                      rms over its dim entries (eps inside the root), multiplied by a weight shared by all
+//                      heads and maps, and its first rot_dims entries are rotated (entry i with entry
+//                      i + rot_dims / 2 by the angle position * freq[i]; cos and sin times a magnitude);
+//                      queries are written back in place, keys and values go to the token's cache row.
+//                      Statistics, angles, cos and sin are float32 whatever the storage type.
+// mu_mapped_attention  per (token, head): softmax attention of each map over the keys the token sees
+//                      (positions max(0, p - window + 1) .. p; window 0: all of 0 .. p), both maps over the
+//                      same values.  With two maps the result is a1 - lambda * a2, brought to unit rms over
+//                      the head's vdim entries and multiplied by out_scale.  Scores, softmax and sums are
+//                      float32.  Which warp takes which keys depends on the token's position only, so a
+//                      token's result does not depend on the step it ran in.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace mu {
+
+constexpr int MA_WARPS = 4;
+constexpr int MA_VPL = 8;          // value entries per lane: vdim <= 256
+
+template <typename TE>
+__global__ void __launch_bounds__(128)
+qk_prepare_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, long long ldk,
+                  const TE* __restrict__ v, long long ldv, const float* __restrict__ q_weight,
+                  const float* __restrict__ k_weight, const float* __restrict__ freqs, float magnitude,
+                  int rot_dims, float eps, int n_heads, int n_kv_heads, int maps, int dim, int vdim,
+                  const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                  const int* __restrict__ block_table, int max_pages, int page_tokens, TE* __restrict__ rows) {
+    extern __shared__ float staged[];                       // [warps][dim]
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int pos = tok_pos[t];
+    const int half = rot_dims / 2;
+    const int n_q = n_heads * maps, n_k = k ? n_kv_heads * maps : 0;
+    const long long width = (long long)n_kv_heads * (maps * dim + vdim);
+    TE* row = nullptr;
+    if (k) {
+        const long long page = block_table[(long long)tok_seq[t] * max_pages + pos / page_tokens];
+        row = rows + (page * page_tokens + pos % page_tokens) * width;
+    }
+    float* mine = staged + warp * dim;
+    for (int item = warp; item < n_q + n_k; item += warps) {
+        const bool is_q = item < n_q;
+        const int slice = is_q ? item : item - n_q;
+        const TE* src = is_q ? q + (long long)t * ldq + (long long)slice * dim : k + (long long)t * ldk + (long long)slice * dim;
+        TE* dst = is_q ? q + (long long)t * ldq + (long long)slice * dim : row + (long long)slice * dim;
+        const float* weight = is_q ? q_weight : k_weight;
+        float ss = 0.0f;
+        for (int d = lane; d < dim; d += 32) {
+            const float x = to_float(src[d]);
+            mine[d] = x;
+            ss += x * x;
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+        __syncwarp();
+        for (int d = lane; d < dim; d += 32) {
+            float y;
+            if (d < rot_dims) {
+                const int i = d < half ? d : d - half;
+                const float a = mine[i] * inv * weight[i], b = mine[i + half] * inv * weight[i + half];
+                float sn, cs;
+                sincosf((float)pos * freqs[i], &sn, &cs);
+                sn *= magnitude;
+                cs *= magnitude;
+                y = d < half ? a * cs - b * sn : b * cs + a * sn;
+            } else {
+                y = mine[d] * inv * weight[d];
+            }
+            dst[d] = from_float<TE>(y);
+        }
+        __syncwarp();
+    }
+    if (v) {
+        TE* vdst = row + (long long)n_kv_heads * maps * dim;
+        const TE* vsrc = v + (long long)t * ldv;
+        for (int d = threadIdx.x; d < n_kv_heads * vdim; d += blockDim.x) vdst[d] = vsrc[d];
+    }
+}
+
+template <typename TE>
+__device__ __forceinline__ float dot_key(const float* qs, const TE* key, int dim, bool vec);
+
+template <>
+__device__ __forceinline__ float dot_key<float>(const float* qs, const float* key, int dim, bool vec) {
+    float s = 0.0f;
+    if (vec) {
+        for (int d = 0; d < dim; d += 4) {
+            const float4 kk = *reinterpret_cast<const float4*>(key + d);
+            s = fmaf(qs[d], kk.x, s);
+            s = fmaf(qs[d + 1], kk.y, s);
+            s = fmaf(qs[d + 2], kk.z, s);
+            s = fmaf(qs[d + 3], kk.w, s);
+        }
+    } else {
+        for (int d = 0; d < dim; ++d) s = fmaf(qs[d], key[d], s);
+    }
+    return s;
+}
+
+template <>
+__device__ __forceinline__ float dot_key<__nv_bfloat16>(const float* qs, const __nv_bfloat16* key, int dim, bool vec) {
+    float s = 0.0f;
+    if (vec) {
+        for (int d = 0; d < dim; d += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(key + d);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p[i]);
+                s = fmaf(qs[d + 2 * i], f.x, s);
+                s = fmaf(qs[d + 2 * i + 1], f.y, s);
+            }
+        }
+    } else {
+        for (int d = 0; d < dim; ++d) s = fmaf(qs[d], __bfloat162float(key[d]), s);
+    }
+    return s;
+}
+
+// One block per (token, head).  A warp takes every MA_WARPS-th run of 32 keys, counted from the first key the
+// token sees: a lane computes the scores of one key (both maps), the warp keeps a running maximum and sum per
+// map, and the lanes share the value entries for the weighted sums.  The warps' parts meet in shared memory.
+template <typename TE, int MAPS>
+__global__ void __launch_bounds__(MA_WARPS * 32)
+mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __restrict__ rows,
+                        const int* __restrict__ block_table, int max_pages, int page_tokens,
+                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
+                        int n_kv_heads, int dim, int vdim, float scale, int window, float lambda, float out_scale,
+                        float eps, int unit_rms, int vec, TE* __restrict__ out, long long ldo) {
+    extern __shared__ float smem[];
+    float* qs = smem;                                        // [MAPS][dim]
+    float* part_acc = qs + MAPS * dim;                       // [warps][MAPS][vdim]
+    float* part_ml = part_acc + MA_WARPS * MAPS * vdim;      // [warps][MAPS][2]
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = h / (n_heads / n_kv_heads);
+    const int pos = tok_pos[t];
+    const int* pages = block_table + (long long)tok_seq[t] * max_pages;
+    const long long width = (long long)n_kv_heads * (MAPS * dim + vdim);
+    const long long key_off = (long long)g * MAPS * dim, val_off = (long long)n_kv_heads * MAPS * dim + (long long)g * vdim;
+    for (int d = threadIdx.x; d < MAPS * dim; d += blockDim.x)
+        qs[d] = to_float(q[(long long)t * ldq + (long long)h * MAPS * dim + d]);
+    __syncthreads();
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    float m_run[MAPS], l_run[MAPS], acc[MAPS][MA_VPL];
+#pragma unroll
+    for (int a = 0; a < MAPS; ++a) {
+        m_run[a] = -INFINITY;
+        l_run[a] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MA_VPL; ++i) acc[a][i] = 0.0f;
+    }
+    for (int base = first + warp * 32; base <= pos; base += MA_WARPS * 32) {
+        const int j = base + lane;
+        const bool live = j <= pos;
+        const TE* row = nullptr;
+        float s[MAPS];
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) s[a] = -INFINITY;
+        if (live) {
+            row = rows + ((long long)pages[j / page_tokens] * page_tokens + j % page_tokens) * width;
+#pragma unroll
+            for (int a = 0; a < MAPS; ++a) s[a] = dot_key<TE>(qs + a * dim, row + key_off + a * dim, dim, vec != 0) * scale;
+        }
+        float p[MAPS];
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+            const float m_new = fmaxf(m_run[a], warp_max(s[a]));
+            const float corr = expf(m_run[a] - m_new);       // 0 at the first run (m_run is -inf, m_new finite)
+            p[a] = live ? expf(s[a] - m_new) : 0.0f;
+            l_run[a] = l_run[a] * corr + warp_sum(p[a]);
+            m_run[a] = m_new;
+#pragma unroll
+            for (int i = 0; i < MA_VPL; ++i) acc[a][i] *= corr;
+        }
+        const int n_live = min(32, pos - base + 1);
+        const unsigned long long mine = (unsigned long long)(uintptr_t)row;
+        for (int jj = 0; jj < n_live; ++jj) {
+            const TE* vrow = reinterpret_cast<const TE*>((uintptr_t)__shfl_sync(0xffffffffu, mine, jj)) + val_off;
+            float pj[MAPS];
+#pragma unroll
+            for (int a = 0; a < MAPS; ++a) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
+#pragma unroll
+            for (int i = 0; i < MA_VPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < vdim) {
+                    const float x = to_float(vrow[d]);
+#pragma unroll
+                    for (int a = 0; a < MAPS; ++a) acc[a][i] = fmaf(pj[a], x, acc[a][i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < MAPS; ++a) {
+        if (lane == 0) {
+            part_ml[(warp * MAPS + a) * 2] = m_run[a];
+            part_ml[(warp * MAPS + a) * 2 + 1] = l_run[a];
+        }
+#pragma unroll
+        for (int i = 0; i < MA_VPL; ++i) {
+            const int d = lane + 32 * i;
+            if (d < vdim) part_acc[(warp * MAPS + a) * vdim + d] = acc[a][i];
+        }
+    }
+    __syncthreads();
+    // the warps' parts in warp order; then the maps' difference and the head's unit rms
+    float sq = 0.0f;
+    for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+        float o[MAPS];
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+            float top = -INFINITY;
+            for (int w = 0; w < MA_WARPS; ++w) top = fmaxf(top, part_ml[(w * MAPS + a) * 2]);
+            float num = 0.0f, den = 0.0f;
+            for (int w = 0; w < MA_WARPS; ++w) {
+                const float mw = part_ml[(w * MAPS + a) * 2];
+                const float f = mw == -INFINITY ? 0.0f : expf(mw - top);
+                num += part_acc[(w * MAPS + a) * vdim + d] * f;
+                den += part_ml[(w * MAPS + a) * 2 + 1] * f;
+            }
+            o[a] = num / den;
+        }
+        const float r = MAPS == 2 ? o[0] - lambda * o[MAPS - 1] : o[0];
+        part_acc[d] = r;          // (warp 0, map 0)'s place: each entry is read and written by this thread only
+        sq += r * r;
+    }
+    float mult = out_scale;
+    if (unit_rms) mult *= 1.0f / sqrtf(block_sum(sq, scratch) / (float)vdim + eps);
+    __syncthreads();
+    for (int d = threadIdx.x; d < vdim; d += blockDim.x)
+        out[(long long)t * ldo + (long long)h * vdim + d] = from_float<TE>(part_acc[d] * mult);
+}
+
+}  // namespace mu
+
+// q [T, n_heads * maps * dim] is normed and rotated in place; k [T, n_kv_heads * maps * dim] and
+// v [T, n_kv_heads * vdim] (both may be null: a layer that reads another layer's rows) go to the cache rows.
+MU_EXPORT int mu_qk_prepare(void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
+                            const float* q_weight, const float* k_weight, const float* freqs, float magnitude,
+                            int rot_dims, float eps, int n_tokens, int n_heads, int n_kv_heads, int maps, int dim,
+                            int vdim, const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
+                            int page_tokens, void* rows, int is_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!q || !q_weight || !tok_pos || dim <= 0 || maps < 1 || maps > 2 || rot_dims < 0 || rot_dims % 2 ||
+        rot_dims > dim || (rot_dims > 0 && !freqs) || (k != nullptr) != (v != nullptr))
+        return MU_ERR_BAD_ARGUMENT;
+    if (k && (!k_weight || !tok_seq || !block_table || !rows || page_tokens <= 0)) return MU_ERR_BAD_ARGUMENT;
+    if (dim > 4096) return MU_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 128;
+    const size_t smem = (size_t)(threads / 32) * dim * sizeof(float);
+    typedef __nv_bfloat16 bf;
+    if (is_bf16)
+        return mu::launch_pdl(mu::qk_prepare_kernel<bf>, dim3(n_tokens), dim3(threads), smem, s, 1, (bf*)q, ldq,
+                              (const bf*)k, ldk, (const bf*)v, ldv, q_weight, k_weight, freqs, magnitude, rot_dims, eps,
+                              n_heads, n_kv_heads, maps, dim, vdim, tok_pos, tok_seq, block_table, max_pages,
+                              page_tokens, (bf*)rows);
+    return mu::launch_pdl(mu::qk_prepare_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, 1, (float*)q, ldq,
+                          (const float*)k, ldk, (const float*)v, ldv, q_weight, k_weight, freqs, magnitude, rot_dims,
+                          eps, n_heads, n_kv_heads, maps, dim, vdim, tok_pos, tok_seq, block_table, max_pages,
+                          page_tokens, (float*)rows);
+}
+
+MU_EXPORT int mu_mapped_attention(const void* q, long long ldq, const void* rows, const int* block_table,
+                                  int max_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
+                                  int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale,
+                                  int window, float lambda, float out_scale, float eps, int unit_rms, void* out,
+                                  long long ldo, int is_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || n_heads <= 0 || n_kv_heads <= 0 ||
+        n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || window < 0)
+        return MU_ERR_BAD_ARGUMENT;
+    if (vdim > 32 * mu::MA_VPL) return MU_ERR_UNSUPPORTED_SIZE;
+    const size_t smem = ((size_t)maps * dim + (size_t)mu::MA_WARPS * maps * (vdim + 2)) * sizeof(float);
+    if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
+    // 16-byte pieces of a key: every slice of a row must start on such a boundary
+    const int per = is_bf16 ? 8 : 4;
+    const int vec = dim % per == 0 && (n_kv_heads * vdim) % per == 0 && ((uintptr_t)rows & 15) == 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_tokens, n_heads), block(mu::MA_WARPS * 32);
+    typedef __nv_bfloat16 bf;
+#define MU_MAPPED(TE, M)                                                                                              \
+    return mu::launch_pdl(mu::mapped_attention_kernel<TE, M>, grid, block, smem, s, 1, (const TE*)q, ldq,             \
+                          (const TE*)rows, block_table, max_pages, page_tokens, tok_pos, tok_seq, n_heads, n_kv_heads, \
+                          dim, vdim, scale, window, lambda, out_scale, eps, unit_rms, vec, (TE*)out, ldo)
+    if (is_bf16) {
+        if (maps == 2) MU_MAPPED(bf, 2);
+        MU_MAPPED(bf, 1);
+    }
+    if (maps == 2) MU_MAPPED(float, 2);
+    MU_MAPPED(float, 1);
+#undef MU_MAPPED
+}

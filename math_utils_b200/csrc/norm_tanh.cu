@@ -45,6 +45,35 @@ __global__ void rms_norm_kernel(const TI* __restrict__ x, long long ldx, const f
     for (int d = threadIdx.x; d < n; d += blockDim.x) dst[d] = from_float<TO>(to_float(src[d]) * inv * w[d]);
 }
 
+// y (+)= scale * x / sqrt(mean(x^2) + eps) * (offset + w) for float32 rows (optionally the rows that `rows` picks):
+// a norm on a sublayer's output that joins the residual stream with a multiplier, or a norm whose weight is
+// stored around zero (offset 1).  `copy` (optional, bfloat16) receives what y then holds: the next sublayer's
+// input in the compute dtype, without a pass of its own.
+template <typename TO, bool ADD>
+__global__ void rms_norm_out_kernel(const float* __restrict__ x, long long ldx, const int* __restrict__ rows,
+                                    const float* __restrict__ w, float offset, float scale, float eps,
+                                    TO* __restrict__ y, long long ldy, __nv_bfloat16* __restrict__ copy, long long ldc,
+                                    int n) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* src = x + (rows ? (long long)rows[r] : (long long)r) * ldx;
+    TO* dst = y + (long long)r * ldy;
+    float s = 0.0f;
+    for (int d = threadIdx.x; d < n; d += blockDim.x) {
+        const float v = src[d];
+        s += v * v;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)n + eps);
+    for (int d = threadIdx.x; d < n; d += blockDim.x) {
+        float v = src[d] * inv * (offset + w[d]) * scale;
+        if (ADD) v += to_float(dst[d]);
+        dst[d] = from_float<TO>(v);
+        if (copy) copy[(long long)r * ldc + d] = __float2bfloat16_rn(v);
+    }
+}
+
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ o, long long ldo, const T* __restrict__ g, long long ldg,
                                     int n_rows, int width) {
@@ -100,6 +129,25 @@ MU_EXPORT int mu_rms_norm(const void* x, long long ldx, int x_bf16, const float*
     if (y_bf16)
         return mu::launch_pdl(mu::rms_norm_kernel<float, bf>, grid, block, 0, s, 1, (const float*)x, ldx, w, (bf*)y, ldy, n, eps);
     return mu::launch_pdl(mu::rms_norm_kernel<float, float>, grid, block, 0, s, 1, (const float*)x, ldx, w, (float*)y, ldy, n, eps);
+}
+
+// y (+)= scale * rms_norm(x) * (offset + w); x float32, y float32 or bfloat16 (add: float32 only).
+MU_EXPORT int mu_rms_norm_out(const float* x, long long ldx, const int* rows, const float* w, float offset, float scale,
+                              float eps, void* y, long long ldy, int y_bf16, int add, void* copy, long long ldc,
+                              int n_rows, int n, void* stream) {
+    if (n_rows <= 0) return MU_OK;
+    if (n <= 0 || !x || !w || !y || (add && y_bf16)) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_rows), block(n >= 1024 ? 256 : 128);
+    typedef __nv_bfloat16 bf;
+    if (y_bf16)
+        return mu::launch_pdl(mu::rms_norm_out_kernel<bf, false>, grid, block, 0, s, 1, x, ldx, rows, w, offset, scale, eps,
+                              (bf*)y, ldy, (bf*)copy, ldc, n);
+    if (add)
+        return mu::launch_pdl(mu::rms_norm_out_kernel<float, true>, grid, block, 0, s, 1, x, ldx, rows, w, offset, scale,
+                              eps, (float*)y, ldy, (bf*)copy, ldc, n);
+    return mu::launch_pdl(mu::rms_norm_out_kernel<float, false>, grid, block, 0, s, 1, x, ldx, rows, w, offset, scale, eps,
+                          (float*)y, ldy, (bf*)copy, ldc, n);
 }
 
 // o[r, c] *= sigmoid(g[r, c]).

@@ -17,6 +17,7 @@ import torch
 from . import build
 
 ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2}
+GATE_ACT_CODES = {"gelu_new": 1, "gelu": 2, "silu": 3}       # what a gated feed-forward may put on its gate
 
 _ERRORS = {
     1: "bad argument (a size, stride or pointer the kernel cannot take)",
@@ -83,6 +84,22 @@ _SIGNATURES = {
                             _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
                                _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p],
+    "mu_embed_pair": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
+                      _c_int, _c_int, _c_p],
+    "mu_rms_norm_out": [_c_p, _c_ll, _c_p, _c_p, _c_f, _c_f, _c_f, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_ll, _c_int,
+                        _c_int, _c_p],
+    "mu_gated_act": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p],
+    "mu_scaled_sum": [_c_p, _c_ll, _c_f, _c_p, _c_ll, _c_f, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
+    "mu_cast_rows": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_p],
+    "mu_qk_prepare": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_int, _c_f, _c_int, _c_int, _c_int,
+                      _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p],
+    "mu_mapped_attention": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                            _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_int, _c_p],
+    "mu_ssd_conv": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll,
+                    _c_int, _c_p, _c_p],
+    "mu_ssd_scan": [_c_p, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
+                    _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p],
+    "mu_gated_group_norm": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_ll, _c_int, _c_p],
     "mu_dynamic_tanh": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_rms_norm": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p],
     "mu_sigmoid_gate": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
@@ -308,6 +325,206 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: Optio
         raise KernelError("rms_norm output has the wrong shape or stride")
     _check(library().mu_rms_norm(_ptr(x), x.stride(0), _is_bf16(x), _ptr(weight), _ptr(out), out.stride(0), _is_bf16(out),
                                  x.shape[0], x.shape[1], float(eps), _stream()), ("rms_norm(n={})", x.shape[1]))
+    return out
+
+
+def rms_norm_out(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float = 0.0, scale: float = 1.0,
+                 out_dtype: Optional[torch.dtype] = None, rows: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, add: bool = False,
+                 copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """scale * x / sqrt(mean(x^2) + eps) * (offset + weight) of float32 rows (optionally the rows that ``rows``
+    picks), written to ``out`` or, with ``add``, added to the float32 ``out``.  ``copy`` (bfloat16, shaped like
+    ``out``) receives what ``out`` then holds."""
+    _need_cuda(x, weight, rows, out, copy)
+    _i32(rows, "rows")
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("rms_norm_out input must be float32 [rows, n] with unit inner stride")
+    if weight.dtype != torch.float32 or not weight.is_contiguous() or weight.numel() != x.shape[1]:
+        raise KernelError("rms_norm_out takes a contiguous float32 weight of n values")
+    n = x.shape[1]
+    n_rows = rows.numel() if rows is not None else x.shape[0]
+    if out is None:
+        if add:
+            raise KernelError("rms_norm_out(add=True) needs the tensor to add to")
+        out = torch.empty((n_rows, n), dtype=out_dtype or torch.float32, device=x.device)
+    if out.shape != (n_rows, n) or out.stride(1) != 1 or (add and out.dtype != torch.float32):
+        raise KernelError("rms_norm_out output has the wrong shape, stride or dtype")
+    if copy is not None and (copy.dtype != torch.bfloat16 or copy.shape != out.shape or copy.stride(1) != 1):
+        raise KernelError("rms_norm_out: the copy is bfloat16 and shaped like the output")
+    _check(library().mu_rms_norm_out(_ptr(x), x.stride(0), _ptr(rows), _ptr(weight), float(offset), float(scale),
+                                     float(eps), _ptr(out), out.stride(0), _is_bf16(out), int(add), _ptr(copy),
+                                     copy.stride(0) if copy is not None else 0, n_rows, n, _stream()),
+           ("rms_norm_out(n={})", n))
+    return out
+
+
+def cast_rows(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 rows [rows, n] as bfloat16."""
+    _need_cuda(x, out)
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("cast_rows takes float32 [rows, n] with unit inner stride")
+    if out is None:
+        out = torch.empty(tuple(x.shape), dtype=torch.bfloat16, device=x.device)
+    if out.dtype != torch.bfloat16 or out.shape != x.shape or out.stride(1) != 1:
+        raise KernelError("cast_rows output must be bfloat16 of the input's shape")
+    _check(library().mu_cast_rows(_ptr(x), x.stride(0), _ptr(out), out.stride(0), x.shape[0], x.shape[1], _stream()),
+           "cast_rows")
+    return out
+
+
+def gated_act(a: torch.Tensor, out: torch.Tensor, act: str) -> torch.Tensor:
+    """out[:, f] = act(a[:, f]) * a[:, F + f] for a [rows, 2F] (gate | up) and out [rows, F] of one dtype."""
+    _need_cuda(a, out)
+    if (a.dim() != 2 or out.dim() != 2 or a.shape[1] != 2 * out.shape[1] or a.shape[0] != out.shape[0]
+            or a.dtype != out.dtype or a.stride(1) != 1 or out.stride(1) != 1):
+        raise KernelError("gated_act takes [rows, 2F] and [rows, F] of one dtype with unit inner stride")
+    if act not in GATE_ACT_CODES:
+        raise KernelError(f"gated_act: no activation '{act}'; known: {', '.join(GATE_ACT_CODES)}")
+    _check(library().mu_gated_act(_ptr(a), a.stride(0), _ptr(out), out.stride(0), out.shape[0], out.shape[1],
+                                  GATE_ACT_CODES[act], _is_bf16(a), _stream()), "gated_act")
+    return out
+
+
+def scaled_sum(p: torch.Tensor, a: float, q: torch.Tensor, b: float, out: torch.Tensor, add: bool = False) -> torch.Tensor:
+    """out (+)= a * p + b * q, all float32 [rows, n]."""
+    _need_cuda(p, q, out)
+    for t in (p, q, out):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or t.shape != out.shape:
+            raise KernelError("scaled_sum takes float32 [rows, n] tensors of one shape with unit inner stride")
+    _check(library().mu_scaled_sum(_ptr(p), p.stride(0), float(a), _ptr(q), q.stride(0), float(b), _ptr(out),
+                                   out.stride(0), out.shape[0], out.shape[1], int(add), _stream()), "scaled_sum")
+    return out
+
+
+def embed_pair(ids: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor, seq_first: torch.Tensor,
+               seq_slots: torch.Tensor, last_token: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor,
+               mul_prev: int, mul_cur: int, single_tokens: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] + pair_table[(previous * mul_prev + ids[t] * mul_cur) mod buckets] as float32, with
+    buckets = pair_table's rows - 1 and that last row for a sequence's first token.  The token before the step's
+    first token of a sequence is ``last_token[slot]``, which is then set to the sequence's last token of the step."""
+    _need_cuda(ids, positions, tok_seq, seq_first, seq_slots, last_token, table, pair_table, out)
+    for t, name in ((ids, "ids"), (positions, "positions"), (tok_seq, "tok_seq"), (seq_first, "seq_first"),
+                    (seq_slots, "seq_slots"), (last_token, "last_token")):
+        _i32(t, name)
+    n, hidden = ids.numel(), table.shape[1]
+    if (pair_table.dtype != table.dtype or pair_table.shape[1] != hidden or not table.is_contiguous()
+            or not pair_table.is_contiguous() or pair_table.shape[0] < 2):
+        raise KernelError("the pair table must match the token table in dtype and width")
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _check(library().mu_embed_pair(_ptr(ids), _ptr(positions), _ptr(tok_seq), _ptr(seq_first), _ptr(seq_slots),
+                                   _ptr(last_token), _ptr(table), _ptr(pair_table), _ptr(out), n, seq_slots.numel(),
+                                   hidden, pair_table.shape[0] - 1, int(mul_prev), int(mul_cur), _is_bf16(table),
+                                   int(single_tokens), _stream()), "embed_pair", launches=1 if single_tokens else 2)
+    return out
+
+
+# ------------------------------------------------------------------ attention over cached rows with score maps
+def qk_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_weight: torch.Tensor,
+               k_weight: Optional[torch.Tensor], freqs: torch.Tensor, magnitude: float, rot_dims: int, eps: float,
+               n_heads: int, n_kv_heads: int, maps: int, dim: int, vdim: int, tok_pos, tok_seq,
+               block_table: Optional[torch.Tensor], page_tokens: int, rows: Optional[torch.Tensor]) -> None:
+    """Unit rms times a weight, then the rotation, for every (head, map) slice of the queries (in place) and of the
+    keys (into the token's cache row, with the values behind them).  ``k`` and ``v`` None: queries only."""
+    _need_cuda(q, k, v, q_weight, k_weight, freqs, tok_pos, tok_seq, block_table, rows)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    if q.stride(1) != 1 or q.shape[1] != n_heads * maps * dim:
+        raise KernelError("qk_prepare: queries are [T, heads * maps * dim] with unit inner stride")
+    if k is not None:
+        if (k.dtype != q.dtype or v.dtype != q.dtype or rows.dtype != q.dtype or k.stride(1) != 1 or v.stride(1) != 1
+                or k.shape[1] != n_kv_heads * maps * dim or v.shape[1] != n_kv_heads * vdim or not rows.is_contiguous()
+                or rows.shape[1] != page_tokens or rows.shape[2] != n_kv_heads * (maps * dim + vdim)):
+            raise KernelError("qk_prepare: keys, values and cache rows do not fit the sizes given")
+    for w in (q_weight, k_weight, freqs):
+        if w is not None and (w.dtype != torch.float32 or not w.is_contiguous()):
+            raise KernelError("qk_prepare: weights and frequencies are contiguous float32")
+    _check(library().mu_qk_prepare(_ptr(q), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0, _ptr(v),
+                                   v.stride(0) if v is not None else 0, _ptr(q_weight), _ptr(k_weight), _ptr(freqs),
+                                   float(magnitude), int(rot_dims), float(eps), q.shape[0], int(n_heads),
+                                   int(n_kv_heads), int(maps), int(dim), int(vdim), _ptr(tok_pos), _ptr(tok_seq),
+                                   _ptr(block_table), block_table.shape[1] if block_table is not None else 0,
+                                   int(page_tokens), _ptr(rows), _is_bf16(q), _stream()),
+           ("qk_prepare(dim={}, maps={})", dim, maps))
+
+
+def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Tensor, page_tokens: int, tok_pos, tok_seq,
+                     n_heads: int, n_kv_heads: int, maps: int, dim: int, vdim: int, scale: float, window: int,
+                     out: torch.Tensor, lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0,
+                     unit_rms: bool = False) -> torch.Tensor:
+    """Softmax attention of every (token, head) over the cached rows it sees (``window`` 0: all up to its own
+    position), one result per score map over the same values; with two maps a1 - lam * a2.  ``unit_rms`` brings
+    each head's result to unit rms (eps inside the root); ``out_scale`` multiplies it."""
+    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    if (q.dtype != rows.dtype or out.dtype != rows.dtype or q.stride(1) != 1 or out.stride(1) != 1
+            or not rows.is_contiguous() or rows.shape[2] != n_kv_heads * (maps * dim + vdim)
+            or q.shape[1] != n_heads * maps * dim or out.shape[1] != n_heads * vdim):
+        raise KernelError("mapped_attention: queries, rows and output do not fit the sizes given")
+    _check(library().mu_mapped_attention(_ptr(q), q.stride(0), _ptr(rows), _ptr(block_table), block_table.shape[1],
+                                         int(page_tokens), _ptr(tok_pos), _ptr(tok_seq), q.shape[0], int(n_heads),
+                                         int(n_kv_heads), int(maps), int(dim), int(vdim), float(scale), int(window),
+                                         float(lam), float(out_scale), float(eps), int(unit_rms), _ptr(out),
+                                         out.stride(0), _is_bf16(rows), _stream()),
+           ("mapped_attention(heads={}/{}, maps={}, dim={}, vdim={})", n_heads, n_kv_heads, maps, dim, vdim))
+    return out
+
+
+# ------------------------------------------------------------------ state-space mixer
+def ssd_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], tok_seq, seq_first, seq_slots,
+             state: torch.Tensor, single_tokens: bool, out: torch.Tensor) -> torch.Tensor:
+    """silu of the short causal convolution of the channels ``u`` [T, channels] per sequence, float32 ``out``; the
+    inputs before a sequence's first token of the step come from the head of ``state[slot]``, which is moved on."""
+    _need_cuda(u, weight, bias, tok_seq, seq_first, seq_slots, state, out)
+    for t, name in ((tok_seq, "tok_seq"), (seq_first, "seq_first"), (seq_slots, "seq_slots")):
+        _i32(t, name)
+    channels, taps = weight.shape
+    if (u.stride(1) != 1 or u.shape[1] != channels or weight.dtype != torch.float32 or not weight.is_contiguous()
+            or out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (u.shape[0], channels)
+            or state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] < (taps - 1) * channels):
+        raise KernelError("ssd_conv: inputs, weight, state or output do not fit")
+    _check(library().mu_ssd_conv(_ptr(u), u.stride(0), _is_bf16(u), _ptr(weight), _ptr(bias), channels, taps, u.shape[0],
+                                 seq_slots.numel(), _ptr(tok_seq), _ptr(seq_first), _ptr(seq_slots), _ptr(state),
+                                 state.stride(0), int(single_tokens), _ptr(out), _stream()), "ssd_conv",
+           launches=1 if single_tokens or taps == 1 else 2)
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias, a_log, skip, n_heads: int, head_dim: int, n_state: int,
+             groups: int, seq_first, seq_slots, state: torch.Tensor, state_offset: int, out: torch.Tensor) -> torch.Tensor:
+    """The recurrence S = exp(-exp(A) dt) S + dt B x^T, y = S^T C + D x per (sequence, head) over the step's tokens,
+    from and to ``state[slot][state_offset:]``; ``xbc`` [T, heads * P + 2 * groups * N] float32 = x | B | C."""
+    _need_cuda(xbc, dt_raw, dt_bias, a_log, skip, seq_first, seq_slots, state, out)
+    inner = n_heads * head_dim
+    if (xbc.dtype != torch.float32 or not xbc.is_contiguous() or xbc.shape[1] != inner + 2 * groups * n_state
+            or dt_raw.stride(1) != 1 or dt_raw.shape[1] != n_heads or out.dtype != torch.float32
+            or not out.is_contiguous() or out.shape != (xbc.shape[0], inner) or state.dtype != torch.float32
+            or state.shape[1] < state_offset + inner * n_state):
+        raise KernelError("ssd_scan: inputs, state or output do not fit")
+    for t in (dt_bias, a_log, skip):
+        if t.dtype != torch.float32 or t.numel() != n_heads or not t.is_contiguous():
+            raise KernelError("ssd_scan: one float32 per head for dt_bias, A_log and D")
+    _check(library().mu_ssd_scan(_ptr(xbc), xbc.shape[1], _ptr(dt_raw), dt_raw.stride(0), _is_bf16(dt_raw), _ptr(dt_bias),
+                                 _ptr(a_log), _ptr(skip), seq_slots.numel(), int(n_heads), int(head_dim), int(n_state),
+                                 int(groups), _ptr(seq_first), _ptr(seq_slots), _ptr(state), state.stride(0),
+                                 int(state_offset), _ptr(out), _stream()),
+           ("ssd_scan(heads={}, P={}, N={})", n_heads, head_dim, n_state))
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
+                     out: torch.Tensor) -> torch.Tensor:
+    """out = unit_rms_per_part(y * silu(z)) * weight: ``y`` float32, ``z`` and ``out`` in the compute dtype."""
+    _need_cuda(y, z, weight, out)
+    inner = y.shape[1]
+    if (y.dtype != torch.float32 or y.stride(1) != 1 or z.stride(1) != 1 or out.stride(1) != 1 or z.dtype != out.dtype
+            or z.shape != y.shape or out.shape != y.shape or weight.dtype != torch.float32 or weight.numel() != inner
+            or inner % parts):
+        raise KernelError("gated_group_norm: inputs do not fit")
+    _check(library().mu_gated_group_norm(_ptr(y), y.stride(0), _ptr(z), z.stride(0), _ptr(weight), y.shape[0], inner,
+                                         int(parts), float(eps), _ptr(out), out.stride(0), _is_bf16(out), _stream()),
+           "gated_group_norm")
     return out
 
 

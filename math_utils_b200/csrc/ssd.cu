@@ -1,0 +1,224 @@
+// A state-space mixer with a matrix state per head (the state-space-duality form), token by token.
+//
+// Per sequence the mixer keeps, in float32, the last taps - 1 inputs of its short convolution and per head a
+// state S [N][P]:
+//     state[slot] = [ conv tail: (taps - 1) x channels, oldest first | S: heads x N x P ]
+// mu_ssd_conv   out[t][c] = silu(bias[c] + sum_j w[c][j] in[t - taps + 1 + j][c]) over the step's tokens of
+//               each sequence, the inputs before the step's first token taken from the tail (zeros when the
+//               sequence starts: a slot's state is cleared when it is taken); float32 out.
+//               When every sequence brings one token the same launch moves the tail on; otherwise
+//               mu_ssd_conv_tail does, after it.
+// mu_ssd_scan   per (sequence, head), the step's tokens in order:
+//               dt = softplus(dt_raw + dt_bias), S = exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x;
+//               everything float32; head h reads B and C of group h / (heads / groups).
+// mu_gated_group_norm   y * silu(z), unit rms over each of `parts` equal parts of the row (eps inside the
+//               root), times a weight; output in the compute dtype.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace mu {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+
+// seq_first[s] .. seq_first[s + 1] - 1 are the flat tokens of the step's s-th sequence.
+template <typename TE>
+__global__ void ssd_conv_kernel(const TE* __restrict__ u, long long ldu, const float* __restrict__ weight,
+                                const float* __restrict__ bias, int channels, int taps, int n_tokens,
+                                const int* __restrict__ tok_seq, const int* __restrict__ seq_first,
+                                const int* __restrict__ seq_slots, float* __restrict__ state, long long state_stride,
+                                int move_tail, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_tokens * channels) return;
+    const int t = (int)(idx / channels), c = (int)(idx % channels);
+    const int s = tok_seq[t];
+    const int first = seq_first[s];
+    float* tail = state + (long long)seq_slots[s] * state_stride;
+    float acc = bias ? bias[c] : 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int li = t - first - (taps - 1) + j;                 // index within the step's tokens of this sequence
+        const float x = li >= 0 ? to_float(u[(long long)(first + li) * ldu + c])
+                                : tail[(long long)(taps - 1 + li) * channels + c];
+        acc = fmaf(weight[(long long)c * taps + j], x, acc);
+    }
+    out[(long long)t * channels + c] = silu_f(acc);
+    if (move_tail) {                                              // one token per sequence: this thread alone touches tail[.][c]
+        for (int k = 0; k + 1 < taps - 1; ++k) tail[(long long)k * channels + c] = tail[(long long)(k + 1) * channels + c];
+        if (taps > 1) tail[(long long)(taps - 2) * channels + c] = to_float(u[(long long)t * ldu + c]);
+    }
+}
+
+template <typename TE>
+__global__ void ssd_conv_tail_kernel(const TE* __restrict__ u, long long ldu, int channels, int taps, int n_seqs,
+                                     const int* __restrict__ seq_first, const int* __restrict__ seq_slots,
+                                     float* __restrict__ state, long long state_stride) {
+    pdl_trigger();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_seqs * channels) return;
+    const int s = (int)(idx / channels), c = (int)(idx % channels);
+    const int first = seq_first[s], count = seq_first[s + 1] - first;
+    float* tail = state + (long long)seq_slots[s] * state_stride;
+    // in ascending order: entry k takes what lay count entries later, which this thread has not written yet
+    for (int k = 0; k < taps - 1; ++k) {
+        const int li = count - (taps - 1) + k;
+        tail[(long long)k * channels + c] = li >= 0 ? to_float(u[(long long)(first + li) * ldu + c])
+                                                    : tail[(long long)(taps - 1 + li) * channels + c];
+    }
+}
+
+// One block per (sequence, head); thread (p, part) owns the state entries S[n][p] with n = part, part + parts, ...
+// in shared memory, so the update and the product with C need no exchange but the final sum over the parts.
+template <typename TE>
+__global__ void ssd_scan_kernel(const float* __restrict__ xbc, int channels, const TE* __restrict__ dt_raw, long long lddt,
+                                const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                const float* __restrict__ skip, int n_heads, int P, int N, int groups, int parts,
+                                const int* __restrict__ seq_first, const int* __restrict__ seq_slots,
+                                float* __restrict__ state, long long state_stride, long long state_offset,
+                                float* __restrict__ y) {
+    extern __shared__ float smem[];
+    float* S = smem;                       // [N][P]
+    float* Bs = S + N * P;                 // [N]
+    float* Cs = Bs + N;                    // [N]
+    float* xs = Cs + N;                    // [P]
+    float* red = xs + P;                   // [parts][P]
+    pdl_trigger();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int p = tid % P, part = tid / P;
+    const int g = h / (n_heads / groups);
+    const int inner = n_heads * P;
+    const int first = seq_first[s], count = seq_first[s + 1] - first;
+    float* mine = state + (long long)seq_slots[s] * state_stride + state_offset + (long long)h * N * P;
+    for (int e = tid; e < N * P; e += blockDim.x) S[e] = mine[e];
+    const float rate = expf(a_log[h]), bias = dt_bias[h], d_skip = skip[h];
+    __syncthreads();
+    for (int li = 0; li < count; ++li) {
+        const int t = first + li;
+        const float* row = xbc + (long long)t * channels;
+        for (int n = tid; n < N; n += blockDim.x) {
+            Bs[n] = row[inner + g * N + n];
+            Cs[n] = row[inner + groups * N + g * N + n];
+        }
+        for (int i = tid; i < P; i += blockDim.x) xs[i] = row[h * P + i];
+        const float dt = softplus_f(to_float(dt_raw[(long long)t * lddt + h]) + bias);
+        const float decay = expf(-rate * dt);
+        __syncthreads();
+        const float x = xs[p];
+        float acc = 0.0f;
+        for (int n = part; n < N; n += parts) {
+            const float v = fmaf(decay, S[n * P + p], dt * Bs[n] * x);
+            S[n * P + p] = v;
+            acc = fmaf(v, Cs[n], acc);
+        }
+        red[part * P + p] = acc;
+        __syncthreads();
+        if (part == 0) {
+            float sum = 0.0f;
+            for (int k = 0; k < parts; ++k) sum += red[k * P + p];
+            y[(long long)t * inner + h * P + p] = fmaf(d_skip, x, sum);
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < N * P; e += blockDim.x) mine[e] = S[e];
+}
+
+template <typename TE>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __restrict__ z, long long ldz,
+                                        const float* __restrict__ weight, int width, float eps, TE* __restrict__ out,
+                                        long long ldo) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, part = blockIdx.y;
+    const float* ys = y + (long long)t * ldy + (long long)part * width;
+    const TE* zs = z + (long long)t * ldz + (long long)part * width;
+    float sq = 0.0f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        const float v = ys[d] * silu_f(to_float(zs[d]));
+        sq += v * v;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        const float v = ys[d] * silu_f(to_float(zs[d]));
+        out[(long long)t * ldo + (long long)part * width + d] = from_float<TE>(v * inv * weight[(long long)part * width + d]);
+    }
+}
+
+}  // namespace mu
+
+// u: the convolution's input channels of the step's tokens ([T, channels] view of the projection, compute dtype).
+// single_tokens: every sequence of the step brings exactly one token (the tail is moved on by the same launch).
+MU_EXPORT int mu_ssd_conv(const void* u, long long ldu, int u_bf16, const float* weight, const float* bias, int channels,
+                          int taps, int n_tokens, int n_seqs, const int* tok_seq, const int* seq_first,
+                          const int* seq_slots, float* state, long long state_stride, int single_tokens, float* out,
+                          void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!u || !weight || !tok_seq || !seq_first || !seq_slots || !state || !out || channels <= 0 || taps < 1)
+        return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+    const long long total = (long long)n_tokens * channels;
+    const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+    int code = u_bf16 ? mu::launch_pdl(mu::ssd_conv_kernel<bf>, grid, block, 0, s, 1, (const bf*)u, ldu, weight, bias,
+                                       channels, taps, n_tokens, tok_seq, seq_first, seq_slots, state, state_stride,
+                                       single_tokens, out)
+                      : mu::launch_pdl(mu::ssd_conv_kernel<float>, grid, block, 0, s, 1, (const float*)u, ldu, weight,
+                                       bias, channels, taps, n_tokens, tok_seq, seq_first, seq_slots, state,
+                                       state_stride, single_tokens, out);
+    if (code != MU_OK || single_tokens || taps == 1) return code;
+    const long long cells = (long long)n_seqs * channels;
+    const dim3 tail_grid((unsigned)((cells + 255) / 256));
+    return u_bf16 ? mu::launch_pdl(mu::ssd_conv_tail_kernel<bf>, tail_grid, block, 0, s, 1, (const bf*)u, ldu, channels,
+                                   taps, n_seqs, seq_first, seq_slots, state, state_stride)
+                  : mu::launch_pdl(mu::ssd_conv_tail_kernel<float>, tail_grid, block, 0, s, 1, (const float*)u, ldu,
+                                   channels, taps, n_seqs, seq_first, seq_slots, state, state_stride);
+}
+
+MU_EXPORT int mu_ssd_scan(const float* xbc, int channels, const void* dt_raw, long long lddt, int dt_bf16,
+                          const float* dt_bias, const float* a_log, const float* skip, int n_seqs, int n_heads, int P,
+                          int N, int groups, const int* seq_first, const int* seq_slots, float* state,
+                          long long state_stride, long long state_offset, float* y, void* stream) {
+    if (n_seqs <= 0) return MU_OK;
+    if (!xbc || !dt_raw || !dt_bias || !a_log || !skip || !seq_first || !seq_slots || !state || !y || n_heads <= 0 ||
+        P <= 0 || N <= 0 || groups <= 0 || n_heads % groups)
+        return MU_ERR_BAD_ARGUMENT;
+    if (P > 1024) return MU_ERR_UNSUPPORTED_SIZE;
+    int parts = 256 / P;
+    if (parts < 1) parts = 1;
+    if (parts > N) parts = N;
+    const size_t smem = ((size_t)N * P + 2 * (size_t)N + P + (size_t)parts * P) * sizeof(float);
+    typedef __nv_bfloat16 bf;
+    if (smem > 48 * 1024) {
+        if (smem > 200 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
+        const void* fn = dt_bf16 ? (const void*)mu::ssd_scan_kernel<bf> : (const void*)mu::ssd_scan_kernel<float>;
+        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return MU_ERR_LAUNCH;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_seqs, n_heads), block(P * parts);
+    return dt_bf16 ? mu::launch_pdl(mu::ssd_scan_kernel<bf>, grid, block, smem, s, 1, xbc, channels, (const bf*)dt_raw, lddt,
+                                    dt_bias, a_log, skip, n_heads, P, N, groups, parts, seq_first, seq_slots, state,
+                                    state_stride, state_offset, y)
+                   : mu::launch_pdl(mu::ssd_scan_kernel<float>, grid, block, smem, s, 1, xbc, channels,
+                                    (const float*)dt_raw, lddt, dt_bias, a_log, skip, n_heads, P, N, groups, parts,
+                                    seq_first, seq_slots, state, state_stride, state_offset, y);
+}
+
+MU_EXPORT int mu_gated_group_norm(const float* y, long long ldy, const void* z, long long ldz, const float* weight,
+                                  int n_tokens, int inner, int parts, float eps, void* out, long long ldo, int is_bf16,
+                                  void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!y || !z || !weight || !out || inner <= 0 || parts <= 0 || inner % parts) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int width = inner / parts;
+    const dim3 grid(n_tokens, parts), block(width >= 1024 ? 256 : 128);
+    typedef __nv_bfloat16 bf;
+    return is_bf16 ? mu::launch_pdl(mu::gated_group_norm_kernel<bf>, grid, block, 0, s, 1, y, ldy, (const bf*)z, ldz, weight,
+                                    width, eps, (bf*)out, ldo)
+                   : mu::launch_pdl(mu::gated_group_norm_kernel<float>, grid, block, 0, s, 1, y, ldy, (const float*)z, ldz,
+                                    weight, width, eps, (float*)out, ldo);
+}

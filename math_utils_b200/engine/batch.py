@@ -77,6 +77,8 @@ class StepContext:
     workspace: dict = field(default_factory=dict)
     q_tiles: Optional[torch.Tensor] = None  # [n, 2] int32: (first flat token, count <= 64) of each query tile
     q_tiles_wide: Optional[torch.Tensor] = None  # the same in tiles of up to 128 queries
+    seq_first: Optional[torch.Tensor] = None  # [n_seqs + 1] int32: the flat index of each sequence's first token of the step
+    last_tokens: Optional[torch.Tensor] = None  # the cache's [n_slots] int32: the last token each slot was fed
     trace: Optional[object] = None          # callable(name, tensor): told every named intermediate result
     tag: str = ""                           # prefix of the names noted now ("h.3." inside layer run 3)
 
@@ -188,7 +190,7 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
     if max_q_len > 1:
         tiles, wide = cut(TILE_QUERIES), cut(2 * TILE_QUERIES)
     n_tiles, n_wide = (len(tiles), len(wide)) if tiles is not None else (0, 0)
-    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * n_tiles, 2 * n_wide] + [t.size for t in tables]
+    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * n_tiles, 2 * n_wide, n_seqs + 1] + [t.size for t in tables]
     offsets = [0]
     for size in sizes:
         offsets.append(offsets[-1] + -(-size // 4) * 4)       # 16-byte aligned parts
@@ -205,8 +207,10 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
     if n_tiles:
         h[offsets[5]: offsets[5] + 2 * n_tiles] = tiles.reshape(-1)
         h[offsets[6]: offsets[6] + 2 * n_wide] = wide.reshape(-1)
+    h[offsets[7]: offsets[7] + n_seqs] = flat0
+    h[offsets[7] + n_seqs] = n_tokens
     for i, t in enumerate(tables):
-        h[offsets[7 + i]: offsets[7 + i] + t.size] = t.reshape(-1)
+        h[offsets[8 + i]: offsets[8 + i] + t.size] = t.reshape(-1)
     dev = torch.empty(total, dtype=torch.int32, device=runtime.device)
     dev.copy_(host[:total], non_blocking=True)
     ring.mark()
@@ -218,7 +222,8 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
         runtime=runtime, position=position, n_tokens=n_tokens, n_seqs=n_seqs,
         token_ids=part(0, n_tokens), tok_pos=part(1, n_tokens), tok_seq=part(2, n_tokens),
         want_rows=part(3, n_want) if n_want else None,
-        block_tables=[part(7 + i, t.size).view(t.shape) for i, t in enumerate(tables)],
+        block_tables=[part(8 + i, t.size).view(t.shape) for i, t in enumerate(tables)],
+        seq_first=part(7, n_seqs + 1), last_tokens=getattr(cache, "last_tokens", None),
         seq_slots=part(4, n_seqs),
         q_tiles=part(5, 2 * n_tiles).view(n_tiles, 2) if n_tiles else None,
         q_tiles_wide=part(6, 2 * n_wide).view(n_wide, 2) if n_wide else None,

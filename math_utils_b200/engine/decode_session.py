@@ -57,7 +57,7 @@ class DecodeSession:
         n = self.n
         self.kv_bound = int(kv_bound or model.max_positions)
         self.tables_shape = [(n, g.max_pages) for g in cache.kv_groups]
-        sizes = [n, n, n, n, n] + [a * b for a, b in self.tables_shape]
+        sizes = [n, n, n, n, n, n + 1] + [a * b for a, b in self.tables_shape]
         offs = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])]).astype(int)
         self._offs = offs
         self.dev = torch.zeros(int(offs[-1]), dtype=torch.int32, device=dev)
@@ -66,13 +66,14 @@ class DecodeSession:
         h[offs[2]:offs[2] + n] = np.arange(n)            # tok_seq
         h[offs[3]:offs[3] + n] = np.arange(n)            # want_rows: every token's logits
         h[offs[4]:offs[4] + n] = np.asarray(self.slots)
+        h[offs[5]:offs[5] + n + 1] = np.arange(n + 1)    # seq_first: one token per sequence
         self.dev.copy_(self.host)
 
         def part(i, count):
             return self.dev[int(offs[i]): int(offs[i]) + count]
 
         self.token_ids, self.tok_pos = part(0, n), part(1, n)
-        self.block_tables = [part(5 + i, a * b).view(a, b) for i, (a, b) in enumerate(self.tables_shape)]
+        self.block_tables = [part(6 + i, a * b).view(a, b) for i, (a, b) in enumerate(self.tables_shape)]
         self.next_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
         self.next_host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
         self.request_ids = torch.tensor(list(request_ids), dtype=torch.int64, device=dev)
@@ -81,7 +82,8 @@ class DecodeSession:
             runtime=rt, position=model.assembly.position, n_tokens=n, n_seqs=n,
             token_ids=self.token_ids, tok_pos=self.tok_pos, tok_seq=part(2, n), want_rows=part(3, n),
             block_tables=self.block_tables, seq_slots=part(4, n), slots=self.slots, starts=[0] * n,
-            q_lens=[1] * n, max_q_len=1, max_kv_len=self.kv_bound, workspace={})
+            q_lens=[1] * n, max_q_len=1, max_kv_len=self.kv_bound, workspace={},
+            seq_first=part(5, n + 1), last_tokens=getattr(cache, "last_tokens", None))
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._feed_views = None
         self._stream = None
@@ -134,9 +136,9 @@ class DecodeSession:
             rows = self.cache.block_table_rows(g.index, self.slots)
             if self._tables_host[i] is None or not np.array_equal(rows, self._tables_host[i]):
                 self._tables_host[i] = rows.copy()
-                h[offs[5 + i]: offs[5 + i] + rows.size] = rows.reshape(-1)
-                self.dev[int(offs[5 + i]): int(offs[5 + i]) + rows.size].copy_(
-                    self.host[int(offs[5 + i]): int(offs[5 + i]) + rows.size], non_blocking=True)
+                h[offs[6 + i]: offs[6 + i] + rows.size] = rows.reshape(-1)
+                self.dev[int(offs[6 + i]): int(offs[6 + i]) + rows.size].copy_(
+                    self.host[int(offs[6 + i]): int(offs[6 + i]) + rows.size], non_blocking=True)
 
     def feed(self, tokens: Sequence[int], positions: Sequence[int]) -> int:
         """This step's token and position of every sequence; returns the bytes
@@ -234,6 +236,9 @@ class DecodeSession:
                                "writes keys and values at the positions it is given")
         ops = self.model.runtime.ops
         saved = (self.token_ids.clone(), self.tok_pos.clone(), self.draws.clone())
+        # what the slots hold besides keys and values (a recurrence's state, the last token) is moved on by the
+        # set-up run and put back after it: the recorded step is the one that counts
+        state = self.cache.snapshot_state(self.slots) if self.cache.has_running_state else None
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -246,6 +251,8 @@ class DecodeSession:
         else:
             self.graph = self._record_graph(self._run_once, side)
         self.token_ids.copy_(saved[0]); self.tok_pos.copy_(saved[1]); self.draws.copy_(saved[2])
+        if state is not None:
+            self.cache.restore_state(state)
 
     def _record_graph(self, body, side: torch.cuda.Stream) -> torch.cuda.CUDAGraph:
         """Records what ``body`` launches on the side stream.  ``torch.cuda.graph`` would do the same

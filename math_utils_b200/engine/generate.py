@@ -181,7 +181,7 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
         windowed = any(g.spec.window > 0 for g in cache.kv_groups)
         # steps launched and not yet read: two, unless a step that ran ahead of the news of its sequence's end
         # could not be taken back (pages given back by a window; fixed-size state of a slot that is kept)
-        depth = 1 if windowed or (kept_slots is not None and cache.state_groups) else 2
+        depth = 1 if windowed or (kept_slots is not None and cache.has_running_state) else 2
         while live:
             members = list(live)                         # the graph's batch; some may park later
             session = session_for(model, cache, params, len(members))

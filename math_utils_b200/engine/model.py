@@ -67,8 +67,10 @@ class DecoderModel:
         return out
 
     def new_cache(self, max_tokens: int, n_slots: Optional[int] = None) -> SequenceCache:
-        return SequenceCache(self.cache_specs(), max_tokens, self.max_positions, self.runtime.dtype,
-                             self.runtime.device, n_slots=n_slots)
+        cache = SequenceCache(self.cache_specs(), max_tokens, self.max_positions, self.runtime.dtype,
+                              self.runtime.device, n_slots=n_slots)
+        cache.keeps_last_token = bool(getattr(self.assembly.embedding, "keeps_last_token", False))
+        return cache
 
     # ------------------------------------------------------------------- step
     def step(self, cache: SequenceCache, entries: Sequence[StepEntry], trace=None) -> Optional[torch.Tensor]:

@@ -1,9 +1,10 @@
 """The parts a model is put together from, and their registry."""
-from . import attention, block, embedding, feedforward, latent_attention, moe, norm, position  # noqa: F401  (they register themselves)
-from .base import (Arrangement, Embedding, FeedForward, Head, KVCacheSpec, Mixer, Norm, Part,
+from . import (attention, block, embedding, feedforward, latent_attention, mapped_attention, moe, norm, parallel, position,
+               state_space)  # noqa: F401  (they register themselves)
+from .base import (Arrangement, CompositeCacheSpec, Embedding, FeedForward, Head, KVCacheSpec, Mixer, Norm, Part,
                    PositionEncoding, RowCacheSpec, StateCacheSpec, TensorSpec, build_part, known_parts, register_part)
 from .linear import Linear
 
-__all__ = ["Arrangement", "Embedding", "FeedForward", "Head", "KVCacheSpec", "Linear", "Mixer", "Norm",
+__all__ = ["Arrangement", "CompositeCacheSpec", "Embedding", "FeedForward", "Head", "KVCacheSpec", "Linear", "Mixer", "Norm",
            "Part", "PositionEncoding", "RowCacheSpec", "StateCacheSpec", "TensorSpec", "build_part", "known_parts",
            "register_part"]

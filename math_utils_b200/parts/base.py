@@ -75,6 +75,13 @@ class StateCacheSpec:
     n_values: int
 
 
+@dataclass(frozen=True)
+class CompositeCacheSpec:
+    """A mixer made of several mixers side by side: each member keeps what its own spec says (or nothing,
+    None); the mixer gets the members' views in this order."""
+    members: Tuple[Any, ...]
+
+
 class Part:
     """Base of all parts.  ``spec.params`` holds sizes and constants,
     ``spec.tensors`` the file names of the part's tensors."""

@@ -30,6 +30,42 @@ class TokenEmbedding(Embedding):
         return self.runtime.ops.embed(ctx.token_ids, ctx.tok_pos, self.weight, position_table, scale=self.scale)
 
 
+class TokenPairEmbedding(Embedding):
+    """A row per token plus a row of a second table chosen by the token and the one before it:
+    row (previous * mul_prev + token * mul_cur) mod buckets, and row ``buckets`` (the table's last) for the first
+    token of a sequence.  The token before the first token of a step is the sequence's state: the cache keeps
+    it per slot (``StepContext.last_tokens``), and the kernel moves it on."""
+    keeps_last_token = True
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.vocab_size = int(self.param("vocab_size"))
+        self.hidden_size = int(self.param("hidden_size"))
+        self.buckets = int(self.param("buckets"))
+        self.mul_prev, self.mul_cur = int(self.param("mul_prev")), int(self.param("mul_cur"))
+
+    def tensor_specs(self):
+        return (TensorSpec(self.tensor_name("weight"), (self.vocab_size, self.hidden_size), role="table"),
+                TensorSpec(self.tensor_name("pair_weight"), (self.buckets + 1, self.hidden_size), role="table"))
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.weight = tensors[self.tensor_name("weight")]
+        self.pair_weight = tensors[self.tensor_name("pair_weight")]
+
+    def table(self):
+        return self.weight
+
+    def forward(self, ctx, position_table):
+        if position_table is not None:
+            raise ValueError("the token-pair embedding adds no position table")
+        if ctx.last_tokens is None or ctx.seq_first is None:
+            raise ValueError("the token-pair embedding needs the cache's last tokens and the step's sequence starts")
+        return self.runtime.ops.embed_pair(ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_first, ctx.seq_slots,
+                                           ctx.last_tokens, self.weight, self.pair_weight, self.mul_prev, self.mul_cur,
+                                           ctx.is_decode)
+
+
 class TiedHead(Head):
     """Logits = h @ table^T with the token table itself, no bias
     (include/ai/LocalModel.hpp:1938-1940, 3796-3799)."""
@@ -77,5 +113,6 @@ class LinearHead(Head):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)
+register_part("embedding", "token_pair_embedding", TokenPairEmbedding, replace=True)
 register_part("head", "linear_head", LinearHead, replace=True)
 register_part("head", "tied_head", TiedHead, replace=True)

@@ -48,6 +48,41 @@ class DenseFeedForward(FeedForward):
         self.down(u, residual=residual if accumulate else None, out=residual)
 
 
+class GatedFeedForward(FeedForward):
+    """down(act(gate h) * (up h)) with three matrices and no biases; ``activation`` is ``silu``, ``gelu_new`` or
+    ``gelu``.  The gate and up matrices are stacked, so one product gives both halves of a row."""
+    can_overwrite = True
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.hidden_size = int(self.param("hidden_size"))
+        self.inner_size = int(self.param("inner_size"))
+        self.activation = self.param("activation", "silu")
+        if self.activation not in ("silu",) + ACTIVATIONS:
+            raise ConfigError(f"gated_ffn: activation '{self.activation}' is not one of silu, {', '.join(ACTIVATIONS)}")
+
+    def tensor_specs(self):
+        d, i, name = self.hidden_size, self.inner_size, self.tensor_name
+        return (TensorSpec(name("gate_weight"), (i, d)), TensorSpec(name("up_weight"), (i, d)),
+                TensorSpec(name("down_weight"), (d, i), init="residual_projection"))
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        import torch
+        both = torch.cat([tensors[self.tensor_name("gate_weight")], tensors[self.tensor_name("up_weight")]], dim=0)
+        self.gate_up = Linear(both.contiguous(), None, runtime)
+        self.down = Linear(tensors[self.tensor_name("down_weight")], None, runtime)
+
+    def forward(self, h, residual, ctx, accumulate: bool = True) -> None:
+        dt = self.runtime.dtype
+        both = ctx.buffer("gated_ffn.both", (ctx.n_tokens, 2 * self.inner_size), dt)
+        hidden = ctx.buffer("gated_ffn.hidden", (ctx.n_tokens, self.inner_size), dt)
+        self.gate_up(h, out=both)
+        self.runtime.ops.gated_act(both, hidden, self.activation)
+        ctx.note("act", hidden)
+        self.down(hidden, residual=residual if accumulate else None, out=residual)
+
+
 class NoFeedForward(FeedForward):
     """A layer that ends after its mixer."""
     can_overwrite = True
@@ -58,4 +93,5 @@ class NoFeedForward(FeedForward):
 
 
 register_part("feed_forward", "dense_ffn", DenseFeedForward, replace=True)
+register_part("feed_forward", "gated_ffn", GatedFeedForward, replace=True)
 register_part("feed_forward", "none", NoFeedForward, replace=True)

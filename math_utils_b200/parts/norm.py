@@ -6,7 +6,9 @@ root, weight and bias (include/ai/LocalModel.hpp:1355-1367).
 ``dynamic_tanh``: tanh(alpha x) * weight + bias with a learned scalar alpha; no
 mean, no variance, no eps.  Tensors ``weight``, ``bias``, ``alpha`` (a scalar).
 
-``rms_norm``: x / sqrt(mean(x^2) + eps) * weight, statistics in float32."""
+``rms_norm``: scale * x / sqrt(mean(x^2) + eps) * (weight_offset + weight), statistics in float32.
+``weight_offset`` (0 unless given; 1 for a weight stored around zero) and ``scale`` (1 unless given:
+the multiplier with which a normed sublayer output joins the residual stream) are parameters."""
 from __future__ import annotations
 
 from ..config.base import PartSpec
@@ -67,18 +69,28 @@ class RmsNorm(Norm):
         super().__init__(spec)
         self.size = int(self.param("size"))
         self.eps = float(self.param("eps"))
+        self.offset = float(self.param("weight_offset", 0.0))
+        self.scale = float(self.param("scale", 1.0))
 
     def tensor_specs(self):
-        return (TensorSpec(self.tensor_name("weight"), (self.size,), role="vector", init="norm_weight"),)
+        return (TensorSpec(self.tensor_name("weight"), (self.size,), role="vector",
+                           init=self.param("init", "norm_weight")),)
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         self.weight = tensors[self.tensor_name("weight")]
 
     def forward(self, x, rows=None):
-        if rows is not None:
-            x = x.index_select(0, rows.long())
-        return self.runtime.ops.rms_norm(x, self.weight, self.eps, self.runtime.dtype)
+        return self.runtime.ops.rms_norm_out(x, self.weight, self.eps, self.offset, self.scale,
+                                             out_dtype=self.runtime.dtype, rows=rows)
+
+    def forward_float(self, x, out=None):
+        return self.runtime.ops.rms_norm_out(x, self.weight, self.eps, self.offset, self.scale, out=out)
+
+    def add_into(self, y, residual, copy=None) -> None:
+        """residual += norm(y); ``copy`` (bfloat16, shaped like the stream) receives the stream as it then is."""
+        self.runtime.ops.rms_norm_out(y, self.weight, self.eps, self.offset, self.scale, out=residual, add=True,
+                                      copy=copy)
 
 
 register_part("norm", "layer_norm", LayerNorm, replace=True)
@@ -89,6 +101,11 @@ class IdentityNorm(Norm):
     def forward(self, x, rows=None):
         if rows is not None:
             x = x.index_select(0, rows.long())
+        if x.dtype == self.runtime.dtype:
+            return x
+        import torch
+        if x.dtype == torch.float32 and self.runtime.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1:
+            return self.runtime.ops.cast_rows(x)
         return x.to(self.runtime.dtype)
 
 
