@@ -5,6 +5,7 @@
     python bench.py --only decode|prefill [--layers N] [--batch B]     # a small case for a profiler
     python bench.py --only marginal [--batch B]    # each kernel class's share of the recorded decode step
     python bench.py --family forisun [--size s|m] [--batch B] [--steps K]   # Forisun beside GPT-2 at equal size
+    python bench.py --family lusalorn [--size s|m] [--batch B] [--steps K]  # Lusalorn beside GPT-2 at equal size
 
 A "step" is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (BASELINE.json's third configuration) with seeded random
@@ -478,6 +479,41 @@ def forisun_config(size):
     return ours, twin
 
 
+LUSALORN_SIZES = {
+    # width, windowed attention (heads, kv heads, dim of one score map, vdim, window), causal attention beside the
+    # state-space mixer (heads, kv heads, dim, vdim), state-space mixer (heads, head size, state), gated ff, layers
+    "s": (1024, (8, 2, 64, 128, 512), (8, 2, 128, 128), (16, 64, 128), 4096, 4),
+    "m": (2048, (16, 4, 64, 128, 512), (16, 4, 128, 128), (32, 64, 128), 8192, 4),
+}
+
+
+def lusalorn_config(size):
+    """A Lusalorn configuration with layer sizes of a real model's order (random weights): two windowed layers with
+    two score maps (the second reads the first one's keys and values), then two layers of causal attention beside a
+    state-space mixer; and the GPT-2 configuration of equal width, layer count, vocabulary and feed-forward work per
+    token (a gated feed-forward has three matrices where GPT-2's has two), head size 64."""
+    D, (H, G, d, dv, window), (lh, lg, ld, lv), (sh, sp, sn), ff, L = LUSALORN_SIZES[size]
+    windowed = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "mask": {"size": window}, "scale": d ** -0.5, "diff": 0.3,
+                "rot": {"base": 250000.0, "dims": d // 2}}
+    both = {"left": {"heads": lh, "kv_heads": lg, "dim": ld, "vdim": lv, "scale": ld ** -0.5,
+                     "rot": {"base": 1.0e6, "dims": ld, "scaling": {"factor": 8.0, "original": 512, "fast": 32.0, "slow": 1.0}}},
+            "right": {"heads": sh, "vdim": sp, "state": sn, "groups": 1, "conv": 4, "norm_groups": 1},
+            "left_scale": 0.6, "right_scale": 1.1}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = []
+    for i in range(L):
+        if i < L // 2:
+            layers.append({"type": "attention", "mixer": dict(windowed, **({"kv_from": 0} if i else {})), "mlp": mlp})
+        else:
+            layers.append({"type": "parallel", "mixer": both, "mlp": mlp})
+    ours = {"architecture": "Lusalorn", "vocab": FAMILY_VOCAB, "width": D, "residual_mult": 0.3, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+    twin = {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "n_layer": L, "n_embd": D, "n_head": D // 64,
+            "n_inner": ff * 3 // 2, "vocab_size": FAMILY_VOCAB, "n_positions": CONTEXT,
+            "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new"}
+    return ours, twin
+
+
 def stage_times(model, prompts, single_steps=8):
     """Device milliseconds per stage of one eager prompt step and of eager single-token steps (their mean)."""
     import torch
@@ -501,16 +537,17 @@ def stage_times(model, prompts, single_steps=8):
 
 
 def run_family(args):
-    """``--family forisun``: prompt and single-token throughput of Forisun at sizes of a real model's order beside
+    """``--family forisun | lusalorn``: prompt and single-token throughput of that design at sizes of a real model's order beside
     GPT-2 at equal size, the same workload shape as the default run (2 x 1,024-token prompts; a batch from
     512-token prompts towards 1,024).  Prints one JSON line; the default run and its line are not touched."""
     import numpy as np
     from math_utils_b200.sampling import SamplingParams
     pk = peaks()
     rng = np.random.default_rng(0)
-    record = {"family": "forisun", "size": args.size, "batch": args.batch, "steps": args.steps, "dtype": "bfloat16",
+    configs = forisun_config(args.size) if args.family == "forisun" else lusalorn_config(args.size)
+    record = {"family": args.family, "size": args.size, "batch": args.batch, "steps": args.steps, "dtype": "bfloat16",
               "data": "synthetic: random weights, random tokens", "peaks": pk, "models": {}}
-    for name, cfg in zip(("forisun", "gpt2_twin"), forisun_config(args.size)):
+    for name, cfg in zip((args.family, "gpt2_twin"), configs):
         llm = load_random(cfg, temperature=0.0, context=CONTEXT)
         model = llm.model
         pre = [rng.integers(0, FAMILY_VOCAB, size=CONTEXT).tolist() for _ in range(PREFILL_SEQS)]
@@ -694,8 +731,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="with --only decode: tokens per prompt")
     ap.add_argument("--reference-dir", default="", help="with --impl reference: a checkout other than baseline/_ref")
     ap.add_argument("--tokens", type=int, default=0, help="with --config: fewer tokens per request than fill the context")
-    ap.add_argument("--family", default="", choices=["", "forisun"],
-                    help="forisun: that design at sizes of a real model's order beside GPT-2 at equal size")
+    ap.add_argument("--family", default="", choices=["", "forisun", "lusalorn"],
+                    help="that design at sizes of a real model's order beside GPT-2 at equal size")
     ap.add_argument("--size", default="s", choices=sorted(FORISUN_SIZES), help="with --family: which sizes")
     args = ap.parse_args()
     if args.gpus != 1:

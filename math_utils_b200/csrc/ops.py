@@ -47,6 +47,7 @@ def _switch(name: str) -> bool:
 #   MU_B200_LATENT_TC=0   latent attention and the experts' products on CUDA cores instead of mma.sync
 PDL, ATT_TC, PREFILL_TC = _switch("MU_B200_PDL"), _switch("MU_B200_ATT_TC"), _switch("MU_B200_PREFILL_TC")
 LATENT_TC = _switch("MU_B200_LATENT_TC")
+MAPPED_TC = _switch("MU_B200_MAPPED_TC")     # =0: prompt attention with score maps on CUDA cores instead of mma.sync
 
 _c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
 
@@ -95,6 +96,9 @@ _SIGNATURES = {
                       _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p],
     "mu_mapped_attention": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                             _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_int, _c_p],
+    "mu_mapped_attention_mma_fits": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "mu_mapped_attention_mma": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+                                _c_int, _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_p],
     "mu_ssd_conv": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll,
                     _c_int, _c_p, _c_p],
     "mu_ssd_scan": [_c_p, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
@@ -451,10 +455,15 @@ def qk_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
 def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Tensor, page_tokens: int, tok_pos, tok_seq,
                      n_heads: int, n_kv_heads: int, maps: int, dim: int, vdim: int, scale: float, window: int,
                      out: torch.Tensor, lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0,
-                     unit_rms: bool = False) -> torch.Tensor:
+                     unit_rms: bool = False, tiles: Optional[torch.Tensor] = None,
+                     tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """Softmax attention of every (token, head) over the cached rows it sees (``window`` 0: all up to its own
     position), one result per score map over the same values; with two maps a1 - lam * a2.  ``unit_rms`` brings
-    each head's result to unit rms (eps inside the root); ``out_scale`` multiplies it."""
+    each head's result to unit rms (eps inside the root); ``out_scale`` multiplies it.
+
+    ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of runs of tokens of one sequence, as a prompt step
+    has them) sends bfloat16 steps at the sizes ``mu_mapped_attention_mma`` takes to the tensor cores, unless
+    ``tensor_cores`` is false."""
     _need_cuda(q, rows, block_table, tok_pos, tok_seq, out)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -462,6 +471,19 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
             or not rows.is_contiguous() or rows.shape[2] != n_kv_heads * (maps * dim + vdim)
             or q.shape[1] != n_heads * maps * dim or out.shape[1] != n_heads * vdim):
         raise KernelError("mapped_attention: queries, rows and output do not fit the sizes given")
+    if tensor_cores is None:
+        tensor_cores = MAPPED_TC
+    if (tensor_cores and tiles is not None and rows.dtype == torch.bfloat16 and q.stride(0) % 8 == 0
+            and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0
+            and library().mu_mapped_attention_mma_fits(int(n_kv_heads), int(maps), int(dim), int(vdim), int(page_tokens))):
+        _need_cuda(tiles)
+        _i32(tiles, "tiles")
+        _check(library().mu_mapped_attention_mma(
+            _ptr(q), q.stride(0), _ptr(rows), _ptr(block_table), block_table.shape[1], int(page_tokens), _ptr(tok_pos),
+            _ptr(tok_seq), _ptr(tiles), tiles.shape[0], int(n_heads), int(n_kv_heads), int(maps), int(dim), int(vdim),
+            float(scale), int(window), float(lam), float(out_scale), float(eps), int(unit_rms), _ptr(out), out.stride(0),
+            _stream()), ("mapped_attention_mma(heads={}/{}, maps={}, dim={}, vdim={})", n_heads, n_kv_heads, maps, dim, vdim))
+        return out
     _check(library().mu_mapped_attention(_ptr(q), q.stride(0), _ptr(rows), _ptr(block_table), block_table.shape[1],
                                          int(page_tokens), _ptr(tok_pos), _ptr(tok_seq), q.shape[0], int(n_heads),
                                          int(n_kv_heads), int(maps), int(dim), int(vdim), float(scale), int(window),

@@ -79,6 +79,7 @@ class StepContext:
     q_tiles_wide: Optional[torch.Tensor] = None  # the same in tiles of up to 128 queries
     seq_first: Optional[torch.Tensor] = None  # [n_seqs + 1] int32: the flat index of each sequence's first token of the step
     last_tokens: Optional[torch.Tensor] = None  # the cache's [n_slots] int32: the last token each slot was fed
+    stream_copy: Optional[torch.Tensor] = None  # the residual stream in the compute dtype, while an arrangement keeps it current
     trace: Optional[object] = None          # callable(name, tensor): told every named intermediate result
     tag: str = ""                           # prefix of the names noted now ("h.3." inside layer run 3)
 

@@ -120,6 +120,7 @@ class DecoderModel:
 
     def forward(self, ctx, cache: SequenceCache) -> Optional[torch.Tensor]:
         a = self.assembly
+        ctx.stream_copy = None
         x = a.embedding.forward(ctx, a.position.embedding_table())
         if a.embedding_norm is not None:
             x = a.embedding_norm.forward_float(x, out=x)

@@ -23,7 +23,7 @@ import torch
 from .attention import CausalSelfAttention
 from .base import Arrangement, PositionEncoding, register_part
 from .feedforward import DenseFeedForward, NoFeedForward
-from .norm import LayerNorm
+from .norm import IdentityNorm, LayerNorm, RmsNorm
 
 
 class PreNormBlock(Arrangement):
@@ -107,22 +107,43 @@ class PreNormBlock(Arrangement):
 
 
 class SandwichNormBlock(Arrangement):
+    """Where a sublayer reads the stream itself (its input norm is the identity) in bfloat16, the output norm
+    before it hands the stream on in bfloat16 from the launch that added to it (``RmsNorm.add_into(copy=)``), so
+    the stream is not read again just to be rounded; ``ctx.stream_copy`` is that copy while it is current."""
+
     def forward(self, x, layer, ctx, cache, owns_cache: bool) -> None:
         y = ctx.buffer("sublayer.out", tuple(x.shape), torch.float32)
-        h = layer.norm1.forward(x)
+        h = self._input(layer.norm1, x, ctx)
         ctx.note("ln1", h)
         self._sublayer(layer.mixer, y, h, y, ctx, cache, owns_cache)
-        layer.extra["norm1b"].add_into(y, x)
+        self._join(layer.extra["norm1b"], y, x, ctx)
         ctx.note("res1", x)
         if not isinstance(layer.feed_forward, NoFeedForward):
-            h = layer.norm2.forward(x)
+            h = self._input(layer.norm2, x, ctx)
             ctx.note("ln2", h)
             if getattr(layer.feed_forward, "fuses_output_norm", False):
                 layer.feed_forward.forward(h, x, ctx, output_norm=layer.extra["norm2b"])
+                ctx.stream_copy = None
             else:
                 self._sublayer(layer.feed_forward, y, h, y, ctx)
-                layer.extra["norm2b"].add_into(y, x)
+                self._join(layer.extra["norm2b"], y, x, ctx)
         ctx.note("res2", x)
+
+    @staticmethod
+    def _input(norm, x, ctx):
+        if isinstance(norm, IdentityNorm) and ctx.stream_copy is not None:
+            return ctx.stream_copy
+        return norm.forward(x)
+
+    @staticmethod
+    def _join(norm, y, x, ctx) -> None:
+        ctx.stream_copy = None
+        if isinstance(norm, RmsNorm) and norm.runtime.dtype == torch.bfloat16:
+            copy = ctx.buffer("stream.copy", tuple(x.shape), torch.bfloat16)
+            norm.add_into(y, x, copy=copy)
+            ctx.stream_copy = copy
+        else:
+            norm.add_into(y, x)
 
     @staticmethod
     def _sublayer(part, y, *args):

@@ -34,7 +34,9 @@ def _note(kind, used, what):
         OBSERVED[kind] = (used, what)
 
 
-def check_logits(got, want, dtype, what=""):
+def check_logits(got, want, dtype, what="", bf16_rms=None):
+    """``bf16_rms``: another rms bound than BF16_RMS for a design whose layers carry rounding noise differently
+    (the largest-error bound moves with it)."""
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
@@ -51,12 +53,13 @@ def check_logits(got, want, dtype, what=""):
         return
     spread = np.maximum(want.std(axis=-1), 1e-3)
     rms = np.sqrt((diff ** 2).mean(axis=-1))
-    top = bf16_max_bound(want.shape[-1])
-    _note("bfloat16 rms", float((rms / (BF16_RMS * spread)).max()), what)
+    bound = BF16_RMS if bf16_rms is None else bf16_rms
+    top = bf16_max_bound(want.shape[-1]) * bound / BF16_RMS
+    _note("bfloat16 rms", float((rms / (bound * spread)).max()), what)
     _note("bfloat16 max", float((err / (top * spread)).max()), what)
-    bad = (rms > BF16_RMS * spread) | (err > top * spread)
+    bad = (rms > bound * spread) | (err > top * spread)
     assert not bad.any(), (f"{what}: first wrong row {int(np.argmax(bad))} of {len(err)}: rms error "
-                           f"{(rms / spread)[np.argmax(bad)]:.4f} of the row's spread (bound {BF16_RMS}), largest "
+                           f"{(rms / spread)[np.argmax(bad)]:.4f} of the row's spread (bound {bound}), largest "
                            f"{(err / spread)[np.argmax(bad)]:.4f} (bound {top:.4f})")
 
 
