@@ -189,7 +189,7 @@ class LusalornConfig:
                      "norm_groups": int(right["norm_groups"]), "eps": self.norm_eps},
                     {"in": q + "in", "conv": q + "conv", "conv_bias": q + "conv.b", "dt_bias": q + "dt_bias",
                      "A_log": q + "A_log", "D": q + "D", "norm": q + "norm", "out": q + "o"})
-                mixer = PartSpec("parallel", {"left": self._attention(m["left"], p + "mix.left.", 1, 0, 0, True, False),
+                mixer = PartSpec("parallel", {"hidden_size": D, "left": self._attention(m["left"], p + "mix.left.", 1, 0, 0, True, False),
                                               "right": state, "left_scale": float(m["left_scale"]),
                                               "right_scale": float(m["right_scale"])})
             mlp = layer.get("mlp")

@@ -34,12 +34,22 @@ qk_prepare_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, l
                   int rot_dims, float eps, int n_heads, int n_kv_heads, int maps, int dim, int vdim,
                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                   const int* __restrict__ block_table, int max_pages, int page_tokens, TE* __restrict__ rows) {
-    extern __shared__ float staged[];                       // [warps][dim]
+    extern __shared__ float staged[];                       // [warps][dim] | cos [rot_dims / 2] | sin [rot_dims / 2]
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int pos = tok_pos[t];
     const int half = rot_dims / 2;
+    float* cs_tab = staged + warps * dim;
+    float* sn_tab = cs_tab + half;
+    // the token's angles once for all its slices
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * freqs[i], &sn, &cs);
+        cs_tab[i] = cs * magnitude;
+        sn_tab[i] = sn * magnitude;
+    }
+    __syncthreads();
     const int n_q = n_heads * maps, n_k = k ? n_kv_heads * maps : 0;
     const long long width = (long long)n_kv_heads * (maps * dim + vdim);
     TE* row = nullptr;
@@ -48,7 +58,8 @@ qk_prepare_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, l
         row = rows + (page * page_tokens + pos % page_tokens) * width;
     }
     float* mine = staged + warp * dim;
-    for (int item = warp; item < n_q + n_k; item += warps) {
+    // blockIdx.y-th share of the token's slices, a warp a slice
+    for (int item = blockIdx.y * warps + warp; item < n_q + n_k; item += gridDim.y * warps) {
         const bool is_q = item < n_q;
         const int slice = is_q ? item : item - n_q;
         const TE* src = is_q ? q + (long long)t * ldq + (long long)slice * dim : k + (long long)t * ldk + (long long)slice * dim;
@@ -68,10 +79,7 @@ qk_prepare_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, l
             if (d < rot_dims) {
                 const int i = d < half ? d : d - half;
                 const float a = mine[i] * inv * weight[i], b = mine[i + half] * inv * weight[i + half];
-                float sn, cs;
-                sincosf((float)pos * freqs[i], &sn, &cs);
-                sn *= magnitude;
-                cs *= magnitude;
+                const float cs = cs_tab[i], sn = sn_tab[i];
                 y = d < half ? a * cs - b * sn : b * cs + a * sn;
             } else {
                 y = mine[d] * inv * weight[d];
@@ -80,7 +88,7 @@ qk_prepare_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, l
         }
         __syncwarp();
     }
-    if (v) {
+    if (v && blockIdx.y == 0) {
         TE* vdst = row + (long long)n_kv_heads * maps * dim;
         const TE* vsrc = v + (long long)t * ldv;
         for (int d = threadIdx.x; d < n_kv_heads * vdim; d += blockDim.x) vdst[d] = vsrc[d];
@@ -244,6 +252,176 @@ mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
         out[(long long)t * ldo + (long long)h * vdim + d] = from_float<TE>(part_acc[d] * mult);
 }
 
+// Single-token steps.  A block takes one (token, kv head) and every MD_SPLITS-th page of what the token sees
+// (page index modulo MD_SPLITS = blockIdx.z, so the share does not depend on the batch): the page's keys and values
+// of that kv head are staged in shared memory once and serve all query heads of the group, a warp a head, a lane a
+// key for the scores and a lane a value entry for the sums.  Each (token, head, map, share) leaves a maximum, a sum
+// and unnormalised values; mapped_merge_kernel puts the shares together in their order and finishes the head.
+constexpr int MD_SPLITS = 16;
+constexpr int MD_KEYS = 64;         // keys staged at a time: one page
+
+template <typename TE, int MAPS>
+__global__ void __launch_bounds__(128)
+mapped_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restrict__ rows,
+                     const int* __restrict__ block_table, int max_pages, const int* __restrict__ tok_pos,
+                     const int* __restrict__ tok_seq, int n_heads, int n_kv_heads, int dim, int vdim, float scale,
+                     int window, int vec, float* __restrict__ part_acc, float* __restrict__ part_ml) {
+    extern __shared__ __align__(16) unsigned char md_raw[];
+    const int kw = MAPS * dim, rw = kw + vdim;                 // the kv head's entries of a row
+    const int pitch = rw + (vec ? 16 / (int)sizeof(TE) : 1);   // rows start in different banks
+    TE* tile = reinterpret_cast<TE*>(md_raw);                  // [MD_KEYS][pitch]: keys (both maps), then values
+    float* qs = reinterpret_cast<float*>(md_raw + (((size_t)MD_KEYS * pitch * sizeof(TE) + 15) / 16) * 16);   // [group][kw]
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, g = blockIdx.y, share = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
+    const int group = n_heads / n_kv_heads;
+    const int pos = tok_pos[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int page_lo = first / MD_KEYS, page_hi = pos / MD_KEYS;
+    const int* pages = block_table + (long long)tok_seq[t] * max_pages;
+    const long long width = (long long)n_kv_heads * rw;
+    const long long key_off = (long long)g * kw, val_off = (long long)n_kv_heads * kw + (long long)g * vdim;
+    for (int i = tid; i < group * kw; i += blockDim.x)
+        qs[i] = to_float(q[(long long)t * ldq + (long long)g * group * kw + i]);
+    // heads of the group this warp takes: warp, warp + warps, ... (at most MD_HEADS of them)
+    constexpr int MD_HEADS = 4;
+    float m_run[MD_HEADS][MAPS], l_run[MD_HEADS][MAPS], acc[MD_HEADS][MAPS][MA_VPL];
+#pragma unroll
+    for (int u = 0; u < MD_HEADS; ++u)
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+            m_run[u][a] = -INFINITY;
+            l_run[u][a] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < MA_VPL; ++i) acc[u][a][i] = 0.0f;
+        }
+    int pg = page_lo + ((share - page_lo) % MD_SPLITS + MD_SPLITS) % MD_SPLITS;     // the first page >= page_lo of this share
+    for (; pg <= page_hi; pg += MD_SPLITS) {
+        __syncthreads();                                       // the page before is done with (and qs is written)
+        const TE* src = rows + (long long)pages[pg] * MD_KEYS * width;
+        if (vec) {
+            constexpr int E = 16 / (int)sizeof(TE);
+            const int kc = kw / E, vc = vdim / E;
+            for (int i = tid; i < MD_KEYS * (kc + vc); i += blockDim.x) {
+                const int r = i / (kc + vc), c = i % (kc + vc);
+                const TE* from = c < kc ? src + r * width + key_off + c * E : src + r * width + val_off + (c - kc) * E;
+                *reinterpret_cast<uint4*>(tile + r * pitch + c * E) = *reinterpret_cast<const uint4*>(from);
+            }
+        } else {
+            for (int i = tid; i < MD_KEYS * rw; i += blockDim.x) {
+                const int r = i / rw, c = i % rw;
+                tile[r * pitch + c] = c < kw ? src[r * width + key_off + c] : src[r * width + val_off + (c - kw)];
+            }
+        }
+        __syncthreads();
+        const int key0 = pg * MD_KEYS;
+#pragma unroll
+        for (int u = 0; u < MD_HEADS; ++u) {
+            const int hg = warp + u * warps;                   // the head's place in its group
+            if (hg >= group) break;
+#pragma unroll
+            for (int half = 0; half < MD_KEYS / 32; ++half) {
+                const int jl = half * 32 + lane, j = key0 + jl;
+                const bool live = j >= first && j <= pos;
+                if (__ballot_sync(0xffffffffu, live) == 0u) continue;
+                float p[MAPS];
+#pragma unroll
+                for (int a = 0; a < MAPS; ++a) {
+                    const float sc = live ? dot_key<TE>(qs + hg * kw + a * dim, tile + jl * pitch + a * dim, dim, vec != 0) * scale
+                                          : -INFINITY;
+                    const float m_new = fmaxf(m_run[u][a], warp_max(sc));
+                    const float corr = expf(m_run[u][a] - m_new);
+                    p[a] = live ? expf(sc - m_new) : 0.0f;
+                    l_run[u][a] = l_run[u][a] * corr + warp_sum(p[a]);
+                    m_run[u][a] = m_new;
+#pragma unroll
+                    for (int i = 0; i < MA_VPL; ++i) acc[u][a][i] *= corr;
+                }
+                for (int jj = 0; jj < 32; ++jj) {
+                    float pj[MAPS];
+#pragma unroll
+                    for (int a = 0; a < MAPS; ++a) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
+                    const TE* vrow = tile + (half * 32 + jj) * pitch + kw;
+#pragma unroll
+                    for (int i = 0; i < MA_VPL; ++i) {
+                        const int d = lane + 32 * i;
+                        if (d < vdim) {
+                            const float x = to_float(vrow[d]);
+#pragma unroll
+                            for (int a = 0; a < MAPS; ++a) acc[u][a][i] = fmaf(pj[a], x, acc[u][a][i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < MD_HEADS; ++u) {
+        const int hg = warp + u * warps;
+        if (hg >= group) break;
+        const int h = g * group + hg;
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+            const long long item = (((long long)t * n_heads + h) * MAPS + a) * MD_SPLITS + share;
+            if (lane == 0) {
+                part_ml[item * 2] = m_run[u][a];
+                part_ml[item * 2 + 1] = l_run[u][a];
+            }
+#pragma unroll
+            for (int i = 0; i < MA_VPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < vdim) part_acc[item * vdim + d] = acc[u][a][i];
+            }
+        }
+    }
+}
+
+template <typename TE, int MAPS>
+__global__ void __launch_bounds__(128)
+mapped_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_heads, int vdim,
+                    float lambda, float out_scale, float eps, int unit_rms, TE* __restrict__ out, long long ldo) {
+    extern __shared__ float merged[];                        // [vdim]
+    __shared__ float scratch[32];
+    __shared__ float factor[MAPS][MD_SPLITS];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const long long item0 = ((long long)t * n_heads + h) * MAPS * MD_SPLITS;
+    if (threadIdx.x < MAPS) {
+        const int a = threadIdx.x;
+        float top = -INFINITY, den = 0.0f;
+        for (int s = 0; s < MD_SPLITS; ++s) top = fmaxf(top, part_ml[(item0 + a * MD_SPLITS + s) * 2]);
+        for (int s = 0; s < MD_SPLITS; ++s) {
+            const float m = part_ml[(item0 + a * MD_SPLITS + s) * 2];
+            const float f = m == -INFINITY ? 0.0f : expf(m - top);
+            factor[a][s] = f;
+            den += part_ml[(item0 + a * MD_SPLITS + s) * 2 + 1] * f;
+        }
+        for (int s = 0; s < MD_SPLITS; ++s) factor[a][s] /= den;
+    }
+    __syncthreads();
+    float sq = 0.0f;
+    for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+        float o[MAPS];
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+            float num = 0.0f;
+            for (int s = 0; s < MD_SPLITS; ++s)
+                if (factor[a][s] != 0.0f) num += part_acc[(item0 + a * MD_SPLITS + s) * vdim + d] * factor[a][s];
+            o[a] = num;
+        }
+        const float r = MAPS == 2 ? o[0] - lambda * o[MAPS - 1] : o[0];
+        merged[d] = r;
+        sq += r * r;
+    }
+    float mult = out_scale;
+    if (unit_rms) mult *= 1.0f / sqrtf(block_sum(sq, scratch) / (float)vdim + eps);
+    __syncthreads();
+    for (int d = threadIdx.x; d < vdim; d += blockDim.x)
+        out[(long long)t * ldo + (long long)h * vdim + d] = from_float<TE>(merged[d] * mult);
+}
+
 }  // namespace mu
 
 // q [T, n_heads * maps * dim] is normed and rotated in place; k [T, n_kv_heads * maps * dim] and
@@ -261,14 +439,18 @@ MU_EXPORT int mu_qk_prepare(void* q, long long ldq, const void* k, long long ldk
     if (dim > 4096) return MU_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 128;
-    const size_t smem = (size_t)(threads / 32) * dim * sizeof(float);
+    const size_t smem = ((size_t)(threads / 32) * dim + rot_dims) * sizeof(float);
+    // few tokens (single-token steps): a token's slices are spread over several blocks
+    const int items = (n_heads + (k ? n_kv_heads : 0)) * maps;
+    const int shares = n_tokens >= 256 ? 1 : (items + 3) / 4;
+    const dim3 grid(n_tokens, shares);
     typedef __nv_bfloat16 bf;
     if (is_bf16)
-        return mu::launch_pdl(mu::qk_prepare_kernel<bf>, dim3(n_tokens), dim3(threads), smem, s, 1, (bf*)q, ldq,
+        return mu::launch_pdl(mu::qk_prepare_kernel<bf>, grid, dim3(threads), smem, s, 1, (bf*)q, ldq,
                               (const bf*)k, ldk, (const bf*)v, ldv, q_weight, k_weight, freqs, magnitude, rot_dims, eps,
                               n_heads, n_kv_heads, maps, dim, vdim, tok_pos, tok_seq, block_table, max_pages,
                               page_tokens, (bf*)rows);
-    return mu::launch_pdl(mu::qk_prepare_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, 1, (float*)q, ldq,
+    return mu::launch_pdl(mu::qk_prepare_kernel<float>, grid, dim3(threads), smem, s, 1, (float*)q, ldq,
                           (const float*)k, ldk, (const float*)v, ldv, q_weight, k_weight, freqs, magnitude, rot_dims,
                           eps, n_heads, n_kv_heads, maps, dim, vdim, tok_pos, tok_seq, block_table, max_pages,
                           page_tokens, (float*)rows);
@@ -303,4 +485,65 @@ MU_EXPORT int mu_mapped_attention(const void* q, long long ldq, const void* rows
     if (maps == 2) MU_MAPPED(float, 2);
     MU_MAPPED(float, 1);
 #undef MU_MAPPED
+}
+
+// Whether mu_mapped_attention_decode takes these sizes (a staged page and the group's queries fit shared memory).
+MU_EXPORT int mu_mapped_decode_fits(int n_heads, int n_kv_heads, int maps, int dim, int vdim, int page_tokens, int is_bf16) {
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads || page_tokens != mu::MD_KEYS || vdim > 32 * mu::MA_VPL) return 0;
+    const int group = n_heads / n_kv_heads, esize = is_bf16 ? 2 : 4;
+    const size_t smem = (size_t)mu::MD_KEYS * (maps * dim + vdim + 16 / esize) * esize + 16 + (size_t)group * maps * dim * sizeof(float);
+    return group <= 16 && smem <= 160 * 1024;
+}
+
+// Floats of scratch a single-token step needs: part_acc, and after it part_ml.
+MU_EXPORT long long mu_mapped_decode_scratch(int n_tokens, int n_heads, int maps, int vdim) {
+    return (long long)n_tokens * n_heads * maps * mu::MD_SPLITS * (vdim + 2);
+}
+
+// The same attention for steps in which every token is the one token of its sequence: pages shared out over
+// blocks, the query heads of a kv head together; `scratch` holds mu_mapped_decode_scratch floats.  Page of 64.
+MU_EXPORT int mu_mapped_attention_decode(const void* q, long long ldq, const void* rows, const int* block_table,
+                                         int max_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
+                                         int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim,
+                                         float scale, int window, float lambda, float out_scale, float eps, int unit_rms,
+                                         float* scratch, void* out, long long ldo, int is_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || !scratch || n_heads <= 0 || n_kv_heads <= 0 ||
+        n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || window < 0)
+        return MU_ERR_BAD_ARGUMENT;
+    const int group = n_heads / n_kv_heads;
+    if (page_tokens != mu::MD_KEYS || vdim > 32 * mu::MA_VPL || group > 16) return MU_ERR_UNSUPPORTED_SIZE;
+    const int esize = is_bf16 ? 2 : 4, per = 16 / esize;
+    const int vec = dim % per == 0 && vdim % per == 0 && ((uintptr_t)rows & 15) == 0;
+    const int rw = maps * dim + vdim, pitch = rw + (vec ? per : 1);
+    const size_t smem = (((size_t)mu::MD_KEYS * pitch * esize + 15) / 16) * 16 + (size_t)group * maps * dim * sizeof(float);
+    if (smem > 200 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* part_acc = scratch;
+    float* part_ml = scratch + (long long)n_tokens * n_heads * maps * mu::MD_SPLITS * vdim;
+    const int warps = group >= 4 ? 4 : group;                // a warp a head; more than four heads: in turns
+    const dim3 grid(n_tokens, n_kv_heads, mu::MD_SPLITS), block(32 * warps);
+    const dim3 mgrid(n_tokens, n_heads), mblock(vdim > 64 ? 128 : 64);
+    typedef __nv_bfloat16 bf;
+#define MU_MAPPED_DECODE(TE, M)                                                                                        \
+    do {                                                                                                               \
+        auto kernel = mu::mapped_decode_kernel<TE, M>;                                                                 \
+        if (smem > 48 * 1024 &&                                                                                        \
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)       \
+            return MU_ERR_LAUNCH;                                                                                      \
+        const int code = mu::launch_pdl(kernel, grid, block, smem, s, 1, (const TE*)q, ldq, (const TE*)rows,           \
+                                        block_table, max_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim, vdim,      \
+                                        scale, window, vec, part_acc, part_ml);                                        \
+        if (code != MU_OK) return code;                                                                                \
+        return mu::launch_pdl(mu::mapped_merge_kernel<TE, M>, mgrid, mblock, (size_t)vdim * sizeof(float), s, 1,       \
+                              (const float*)part_acc, (const float*)part_ml, n_heads, vdim, lambda, out_scale, eps,    \
+                              unit_rms, (TE*)out, ldo);                                                                \
+    } while (0)
+    if (is_bf16) {
+        if (maps == 2) MU_MAPPED_DECODE(bf, 2);
+        MU_MAPPED_DECODE(bf, 1);
+    }
+    if (maps == 2) MU_MAPPED_DECODE(float, 2);
+    MU_MAPPED_DECODE(float, 1);
+#undef MU_MAPPED_DECODE
 }

@@ -45,32 +45,97 @@ __global__ void rms_norm_kernel(const TI* __restrict__ x, long long ldx, const f
     for (int d = threadIdx.x; d < n; d += blockDim.x) dst[d] = from_float<TO>(to_float(src[d]) * inv * w[d]);
 }
 
-// y (+)= scale * x / sqrt(mean(x^2) + eps) * (offset + w) for float32 rows (optionally the rows that `rows` picks):
-// a norm on a sublayer's output that joins the residual stream with a multiplier, or a norm whose weight is
-// stored around zero (offset 1).  `copy` (optional, bfloat16) receives what y then holds: the next sublayer's
-// input in the compute dtype, without a pass of its own.
+// y (+)= scale * v / sqrt(mean(v^2) + eps) * (offset + w) for float32 rows v = x (optionally the rows that `rows`
+// picks), or v = a * x + b * x2 (two branches that join with a weight each, summed on the way in): a norm on a
+// sublayer's output that joins the residual stream with a multiplier, or a norm whose weight is stored around zero
+// (offset 1).  `copy` (optional, bfloat16) receives what y then holds: the next sublayer's input in the compute
+// dtype, without a pass of its own.
 template <typename TO, bool ADD>
-__global__ void rms_norm_out_kernel(const float* __restrict__ x, long long ldx, const int* __restrict__ rows,
-                                    const float* __restrict__ w, float offset, float scale, float eps,
-                                    TO* __restrict__ y, long long ldy, __nv_bfloat16* __restrict__ copy, long long ldc,
-                                    int n) {
+__global__ void rms_norm_out_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ x2, long long ldx2,
+                                    float a, float b, const int* __restrict__ rows, const float* __restrict__ w,
+                                    float offset, float scale, float eps, TO* __restrict__ y, long long ldy,
+                                    __nv_bfloat16* __restrict__ copy, long long ldc, int n) {
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x;
-    const float* src = x + (rows ? (long long)rows[r] : (long long)r) * ldx;
+    const long long from = rows ? (long long)rows[r] : (long long)r;
+    const float* src = x + from * ldx;
+    const float* src2 = x2 ? x2 + from * ldx2 : nullptr;
     TO* dst = y + (long long)r * ldy;
     float s = 0.0f;
     for (int d = threadIdx.x; d < n; d += blockDim.x) {
-        const float v = src[d];
+        const float v = src2 ? a * src[d] + b * src2[d] : src[d];
         s += v * v;
     }
     const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)n + eps);
     for (int d = threadIdx.x; d < n; d += blockDim.x) {
-        float v = src[d] * inv * (offset + w[d]) * scale;
+        float v = (src2 ? a * src[d] + b * src2[d] : src[d]) * inv * (offset + w[d]) * scale;
         if (ADD) v += to_float(dst[d]);
         dst[d] = from_float<TO>(v);
         if (copy) copy[(long long)r * ldc + d] = __float2bfloat16_rn(v);
+    }
+}
+
+// The same for rows of up to 4,096 values that are whole, aligned 16-byte pieces: a block of 256 threads reads its
+// row once, four values a load, and keeps it in registers between the statistics and the output.
+template <typename TO, bool ADD>
+__global__ void __launch_bounds__(256)
+rms_norm_out_vec_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ x2, long long ldx2,
+                        float a, float b, const int* __restrict__ rows, const float* __restrict__ w, float offset,
+                        float scale, float eps, TO* __restrict__ y, long long ldy, __nv_bfloat16* __restrict__ copy,
+                        long long ldc, int n) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, n4 = n / 4;
+    const long long from = rows ? (long long)rows[r] : (long long)r;
+    const float4* src = reinterpret_cast<const float4*>(x + from * ldx);
+    const float4* src2 = x2 ? reinterpret_cast<const float4*>(x2 + from * ldx2) : nullptr;
+    float4 v[4];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + 256 * i;
+        v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (idx < n4) {
+            v[i] = src[idx];
+            if (src2) {
+                const float4 u = src2[idx];
+                v[i] = make_float4(a * v[i].x + b * u.x, a * v[i].y + b * u.y, a * v[i].z + b * u.z, a * v[i].w + b * u.w);
+            }
+        }
+        s += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+    const float inv = scale / sqrtf(block_sum(s, scratch) / (float)n + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + 256 * i;
+        if (idx < n4) {
+            const float4 g = reinterpret_cast<const float4*>(w)[idx];
+            float4 o = make_float4(v[i].x * inv * (offset + g.x), v[i].y * inv * (offset + g.y),
+                                   v[i].z * inv * (offset + g.z), v[i].w * inv * (offset + g.w));
+            if (ADD) {
+                const float4 old = reinterpret_cast<const float4*>(y + (long long)r * ldy)[idx];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            if (sizeof(TO) == 4) {
+                reinterpret_cast<float4*>(y + (long long)r * ldy)[idx] = o;
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(y + (long long)r * ldy)[idx] = packed;
+            }
+            if (copy) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(copy + (long long)r * ldc)[idx] = packed;
+            }
+        }
     }
 }
 
@@ -131,23 +196,32 @@ MU_EXPORT int mu_rms_norm(const void* x, long long ldx, int x_bf16, const float*
     return mu::launch_pdl(mu::rms_norm_kernel<float, float>, grid, block, 0, s, 1, (const float*)x, ldx, w, (float*)y, ldy, n, eps);
 }
 
-// y (+)= scale * rms_norm(x) * (offset + w); x float32, y float32 or bfloat16 (add: float32 only).
-MU_EXPORT int mu_rms_norm_out(const float* x, long long ldx, const int* rows, const float* w, float offset, float scale,
-                              float eps, void* y, long long ldy, int y_bf16, int add, void* copy, long long ldc,
-                              int n_rows, int n, void* stream) {
+// y (+)= scale * rms_norm(v) * (offset + w) with v = x, or a * x + b * x2 when x2 is given; x, x2 float32, y float32
+// or bfloat16 (add: float32 only).
+MU_EXPORT int mu_rms_norm_out(const float* x, long long ldx, const float* x2, long long ldx2, float a, float b,
+                              const int* rows, const float* w, float offset, float scale, float eps, void* y,
+                              long long ldy, int y_bf16, int add, void* copy, long long ldc, int n_rows, int n,
+                              void* stream) {
     if (n_rows <= 0) return MU_OK;
     if (n <= 0 || !x || !w || !y || (add && y_bf16)) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_rows), block(n >= 1024 ? 256 : 128);
     typedef __nv_bfloat16 bf;
-    if (y_bf16)
-        return mu::launch_pdl(mu::rms_norm_out_kernel<bf, false>, grid, block, 0, s, 1, x, ldx, rows, w, offset, scale, eps,
-                              (bf*)y, ldy, (bf*)copy, ldc, n);
-    if (add)
-        return mu::launch_pdl(mu::rms_norm_out_kernel<float, true>, grid, block, 0, s, 1, x, ldx, rows, w, offset, scale,
-                              eps, (float*)y, ldy, (bf*)copy, ldc, n);
-    return mu::launch_pdl(mu::rms_norm_out_kernel<float, false>, grid, block, 0, s, 1, x, ldx, rows, w, offset, scale, eps,
-                          (float*)y, ldy, (bf*)copy, ldc, n);
+    const bool vec = n % 4 == 0 && n <= 4096 && ldx % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
+                     (!x2 || (ldx2 % 4 == 0 && ((uintptr_t)x2 & 15) == 0)) && ldy % 4 == 0 &&
+                     ((uintptr_t)y & 15) == 0 && (!copy || (ldc % 4 == 0 && ((uintptr_t)copy & 7) == 0));
+    const dim3 grid(n_rows), block(vec ? 256 : (n >= 1024 ? 256 : 128));
+#define MU_RMS_OUT(KERNEL, TO, ADD)                                                                                    \
+    return mu::launch_pdl(mu::KERNEL<TO, ADD>, grid, block, 0, s, 1, x, ldx, x2, ldx2, a, b, rows, w, offset, scale,   \
+                          eps, (TO*)y, ldy, (bf*)copy, ldc, n)
+    if (vec) {
+        if (y_bf16) MU_RMS_OUT(rms_norm_out_vec_kernel, bf, false);
+        if (add) MU_RMS_OUT(rms_norm_out_vec_kernel, float, true);
+        MU_RMS_OUT(rms_norm_out_vec_kernel, float, false);
+    }
+    if (y_bf16) MU_RMS_OUT(rms_norm_out_kernel, bf, false);
+    if (add) MU_RMS_OUT(rms_norm_out_kernel, float, true);
+    MU_RMS_OUT(rms_norm_out_kernel, float, false);
+#undef MU_RMS_OUT
 }
 
 // o[r, c] *= sigmoid(g[r, c]).

@@ -87,8 +87,8 @@ _SIGNATURES = {
                                _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p],
     "mu_embed_pair": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                       _c_int, _c_int, _c_p],
-    "mu_rms_norm_out": [_c_p, _c_ll, _c_p, _c_p, _c_f, _c_f, _c_f, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_ll, _c_int,
-                        _c_int, _c_p],
+    "mu_rms_norm_out": [_c_p, _c_ll, _c_p, _c_ll, _c_f, _c_f, _c_p, _c_p, _c_f, _c_f, _c_f, _c_p, _c_ll, _c_int, _c_int,
+                        _c_p, _c_ll, _c_int, _c_int, _c_p],
     "mu_gated_act": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_scaled_sum": [_c_p, _c_ll, _c_f, _c_p, _c_ll, _c_f, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
     "mu_cast_rows": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_p],
@@ -96,6 +96,10 @@ _SIGNATURES = {
                       _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p],
     "mu_mapped_attention": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                             _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_int, _c_p],
+    "mu_mapped_decode_fits": [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
+    "mu_mapped_decode_scratch": [_c_int, _c_int, _c_int, _c_int],
+    "mu_mapped_attention_decode": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                   _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_p],
     "mu_mapped_attention_mma_fits": [_c_int, _c_int, _c_int, _c_int, _c_int],
     "mu_mapped_attention_mma": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                                 _c_int, _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_p],
@@ -335,11 +339,14 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: Optio
 def rms_norm_out(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float = 0.0, scale: float = 1.0,
                  out_dtype: Optional[torch.dtype] = None, rows: Optional[torch.Tensor] = None,
                  out: Optional[torch.Tensor] = None, add: bool = False,
-                 copy: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """scale * x / sqrt(mean(x^2) + eps) * (offset + weight) of float32 rows (optionally the rows that ``rows``
+                 copy: Optional[torch.Tensor] = None, second=None) -> torch.Tensor:
+    """scale * v / sqrt(mean(v^2) + eps) * (offset + weight) of float32 rows v = x (optionally the rows that ``rows``
     picks), written to ``out`` or, with ``add``, added to the float32 ``out``.  ``copy`` (bfloat16, shaped like
-    ``out``) receives what ``out`` then holds."""
-    _need_cuda(x, weight, rows, out, copy)
+    ``out``) receives what ``out`` then holds.  ``second`` = (a, x2, b): the rows are v = a * x + b * x2."""
+    a, x2, b = second if second is not None else (1.0, None, 0.0)
+    _need_cuda(x, weight, rows, out, copy, x2)
+    if x2 is not None and (x2.dtype != torch.float32 or x2.shape != x.shape or x2.stride(1) != 1):
+        raise KernelError("rms_norm_out: the second input is float32 and shaped like the first")
     _i32(rows, "rows")
     if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
         raise KernelError("rms_norm_out input must be float32 [rows, n] with unit inner stride")
@@ -355,7 +362,8 @@ def rms_norm_out(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: floa
         raise KernelError("rms_norm_out output has the wrong shape, stride or dtype")
     if copy is not None and (copy.dtype != torch.bfloat16 or copy.shape != out.shape or copy.stride(1) != 1):
         raise KernelError("rms_norm_out: the copy is bfloat16 and shaped like the output")
-    _check(library().mu_rms_norm_out(_ptr(x), x.stride(0), _ptr(rows), _ptr(weight), float(offset), float(scale),
+    _check(library().mu_rms_norm_out(_ptr(x), x.stride(0), _ptr(x2), x2.stride(0) if x2 is not None else 0, float(a),
+                                     float(b), _ptr(rows), _ptr(weight), float(offset), float(scale),
                                      float(eps), _ptr(out), out.stride(0), _is_bf16(out), int(add), _ptr(copy),
                                      copy.stride(0) if copy is not None else 0, n_rows, n, _stream()),
            ("rms_norm_out(n={})", n))
@@ -456,14 +464,15 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
                      n_heads: int, n_kv_heads: int, maps: int, dim: int, vdim: int, scale: float, window: int,
                      out: torch.Tensor, lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0,
                      unit_rms: bool = False, tiles: Optional[torch.Tensor] = None,
-                     tensor_cores: Optional[bool] = None) -> torch.Tensor:
+                     tensor_cores: Optional[bool] = None, single_tokens: bool = False) -> torch.Tensor:
     """Softmax attention of every (token, head) over the cached rows it sees (``window`` 0: all up to its own
     position), one result per score map over the same values; with two maps a1 - lam * a2.  ``unit_rms`` brings
     each head's result to unit rms (eps inside the root); ``out_scale`` multiplies it.
 
     ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of runs of tokens of one sequence, as a prompt step
     has them) sends bfloat16 steps at the sizes ``mu_mapped_attention_mma`` takes to the tensor cores, unless
-    ``tensor_cores`` is false."""
+    ``tensor_cores`` is false.  ``single_tokens`` (every token is the one token of its sequence) takes the kernel
+    that shares a sequence's pages out over blocks and lets the query heads of a kv head read them together."""
     _need_cuda(q, rows, block_table, tok_pos, tok_seq, out)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -471,6 +480,19 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
             or not rows.is_contiguous() or rows.shape[2] != n_kv_heads * (maps * dim + vdim)
             or q.shape[1] != n_heads * maps * dim or out.shape[1] != n_heads * vdim):
         raise KernelError("mapped_attention: queries, rows and output do not fit the sizes given")
+    if single_tokens and library().mu_mapped_decode_fits(int(n_heads), int(n_kv_heads), int(maps), int(dim), int(vdim),
+                                                         int(page_tokens), _is_bf16(rows)):
+        lib = library()
+        lib.mu_mapped_decode_scratch.restype = _c_ll
+        need = int(lib.mu_mapped_decode_scratch(q.shape[0], int(n_heads), int(maps), int(vdim)))
+        room = scratch("mapped_decode", q.device, need, torch.float32)
+        _check(lib.mu_mapped_attention_decode(
+            _ptr(q), q.stride(0), _ptr(rows), _ptr(block_table), block_table.shape[1], int(page_tokens), _ptr(tok_pos),
+            _ptr(tok_seq), q.shape[0], int(n_heads), int(n_kv_heads), int(maps), int(dim), int(vdim), float(scale),
+            int(window), float(lam), float(out_scale), float(eps), int(unit_rms), _ptr(room), _ptr(out), out.stride(0),
+            _is_bf16(rows), _stream()),
+            ("mapped_attention_decode(heads={}/{}, maps={}, dim={}, vdim={})", n_heads, n_kv_heads, maps, dim, vdim), launches=2)
+        return out
     if tensor_cores is None:
         tensor_cores = MAPPED_TC
     if (tensor_cores and tiles is not None and rows.dtype == torch.bfloat16 and q.stride(0) % 8 == 0

@@ -8,7 +8,7 @@
 //               sequence starts: a slot's state is cleared when it is taken); float32 out.
 //               When every sequence brings one token the same launch moves the tail on; otherwise
 //               mu_ssd_conv_tail does, after it.
-// mu_ssd_scan   per (sequence, head), the step's tokens in order:
+// mu_ssd_scan   per (sequence, head, a few columns of S), the step's tokens in order:
 //               dt = softplus(dt_raw + dt_bias), S = exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x;
 //               everything float32; head h reads B and C of group h / (heads / groups).
 // mu_gated_group_norm   y * silu(z), unit rms over each of `parts` equal parts of the row (eps inside the
@@ -126,6 +126,122 @@ __global__ void ssd_scan_kernel(const float* __restrict__ xbc, int channels, con
     for (int e = tid; e < N * P; e += blockDim.x) mine[e] = S[e];
 }
 
+// The same recurrence with the state in registers: a block per (sequence, head, 8 columns of S); a half-warp owns
+// one column p and lane i of it the entries S[i + 16 k][p], so a step is NS fused multiply-adds for the update,
+// NS for the product with C and four shuffles, with no barrier.  B, C, x, dt and the decay of 16 steps at a time
+// come through shared memory in two stages (4-byte cp.async, so nothing has to be aligned), the next 16 steps on
+// their way while these are worked on.  N <= 16 * NS, NS up to 8 (larger states take the kernel above).
+constexpr int SC_STEPS = 16, SC_COLS = 8;
+
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+
+template <typename TE, int NS>
+__global__ void __launch_bounds__(128)
+ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __restrict__ dt_raw, long long lddt,
+                     const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ skip,
+                     int n_heads, int P, int N, int groups, const int* __restrict__ seq_first,
+                     const int* __restrict__ seq_slots, float* __restrict__ state, long long state_stride,
+                     long long state_offset, float* __restrict__ y) {
+    constexpr int NPAD = 16 * NS;
+    __shared__ float Bs[2][SC_STEPS][NPAD], Cs[2][SC_STEPS][NPAD], xs[2][SC_STEPS][SC_COLS], dts[2][SC_STEPS],
+        decs[2][SC_STEPS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, part = lane & 15;
+    const int pl = warp * 2 + (lane >> 4);
+    for (int i = tid; i < 2 * SC_STEPS * NPAD; i += blockDim.x) {
+        (&Bs[0][0][0])[i] = 0.0f;
+        (&Cs[0][0][0])[i] = 0.0f;
+    }
+    for (int i = tid; i < 2 * SC_STEPS * SC_COLS; i += blockDim.x) (&xs[0][0][0])[i] = 0.0f;
+    pdl_trigger();
+    pdl_wait();
+    __syncthreads();
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SC_COLS;
+    const int p = col0 + pl;
+    const bool live = p < P;
+    const int g = h / (n_heads / groups);
+    const int inner = n_heads * P;
+    const int first = seq_first[s], count = seq_first[s + 1] - first;
+    float* mine = state + (long long)seq_slots[s] * state_stride + state_offset + (long long)h * N * P;
+    float S[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part + 16 * i;
+        S[i] = (live && n < N) ? mine[(long long)n * P + p] : 0.0f;
+    }
+    const float rate = expf(a_log[h]), bias = dt_bias[h], d_skip = skip[h];
+    const int n_chunks = (count + SC_STEPS - 1) / SC_STEPS;
+
+    auto issue = [&](int chunk, int buf) {
+        const int left = min(SC_STEPS, count - chunk * SC_STEPS);
+        const float* base = xbc + (long long)(first + chunk * SC_STEPS) * channels;
+        for (int i = tid; i < left * N; i += blockDim.x) {
+            const int tt = i / N, n = i % N;
+            const float* row = base + (long long)tt * channels;
+            cp_async4(&Bs[buf][tt][n], row + inner + g * N + n);
+            cp_async4(&Cs[buf][tt][n], row + inner + groups * N + g * N + n);
+        }
+        for (int i = tid; i < left * SC_COLS; i += blockDim.x) {
+            const int tt = i / SC_COLS, c = i % SC_COLS;
+            if (col0 + c < P) cp_async4(&xs[buf][tt][c], base + (long long)tt * channels + h * P + col0 + c);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto raw_dt = [&](int chunk) {
+        const int li = chunk * SC_STEPS + tid;
+        return (tid < SC_STEPS && li < count) ? to_float(dt_raw[(long long)(first + li) * lddt + h]) : 0.0f;
+    };
+    auto put_dt = [&](float raw, int buf) {
+        if (tid < SC_STEPS) {
+            const float dt = softplus_f(raw + bias);
+            dts[buf][tid] = dt;
+            decs[buf][tid] = expf(-rate * dt);
+        }
+    };
+    if (n_chunks > 0) {
+        issue(0, 0);
+        put_dt(raw_dt(0), 0);
+    }
+    for (int c = 0; c < n_chunks; ++c) {
+        const int buf = c & 1;
+        float next_raw = 0.0f;
+        if (c + 1 < n_chunks) {
+            issue(c + 1, buf ^ 1);
+            next_raw = raw_dt(c + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int left = min(SC_STEPS, count - c * SC_STEPS);
+        for (int tt = 0; tt < left; ++tt) {
+            const float x = xs[buf][tt][pl], dt = dts[buf][tt], dec = decs[buf][tt];
+            const float dx = dt * x;
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                const float v = fmaf(dec, S[i], Bs[buf][tt][part + 16 * i] * dx);
+                S[i] = v;
+                acc = fmaf(v, Cs[buf][tt][part + 16 * i], acc);
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            if (part == 0 && live) y[(long long)(first + c * SC_STEPS + tt) * inner + h * P + p] = fmaf(d_skip, x, acc);
+        }
+        if (c + 1 < n_chunks) put_dt(next_raw, buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part + 16 * i;
+        if (live && n < N) mine[(long long)n * P + p] = S[i];
+    }
+}
+
 template <typename TE>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __restrict__ z, long long ldz,
                                         const float* __restrict__ weight, int width, float eps, TE* __restrict__ out,
@@ -186,19 +302,34 @@ MU_EXPORT int mu_ssd_scan(const float* xbc, int channels, const void* dt_raw, lo
     if (!xbc || !dt_raw || !dt_bias || !a_log || !skip || !seq_first || !seq_slots || !state || !y || n_heads <= 0 ||
         P <= 0 || N <= 0 || groups <= 0 || n_heads % groups)
         return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+    if (N <= 128) {                                   // the state in registers, 8 columns of S a block
+        const dim3 grid(n_seqs, n_heads, (P + mu::SC_COLS - 1) / mu::SC_COLS), block(128);
+#define MU_SCAN_COLS(NS)                                                                                               \
+    return dt_bf16 ? mu::launch_pdl(mu::ssd_scan_cols_kernel<bf, NS>, grid, block, 0, s, 1, xbc, channels,             \
+                                    (const bf*)dt_raw, lddt, dt_bias, a_log, skip, n_heads, P, N, groups, seq_first,   \
+                                    seq_slots, state, state_stride, state_offset, y)                                   \
+                   : mu::launch_pdl(mu::ssd_scan_cols_kernel<float, NS>, grid, block, 0, s, 1, xbc, channels,          \
+                                    (const float*)dt_raw, lddt, dt_bias, a_log, skip, n_heads, P, N, groups,           \
+                                    seq_first, seq_slots, state, state_stride, state_offset, y)
+        if (N <= 16) MU_SCAN_COLS(1);
+        if (N <= 32) MU_SCAN_COLS(2);
+        if (N <= 64) MU_SCAN_COLS(4);
+        MU_SCAN_COLS(8);
+#undef MU_SCAN_COLS
+    }
     if (P > 1024) return MU_ERR_UNSUPPORTED_SIZE;
     int parts = 256 / P;
     if (parts < 1) parts = 1;
     if (parts > N) parts = N;
     const size_t smem = ((size_t)N * P + 2 * (size_t)N + P + (size_t)parts * P) * sizeof(float);
-    typedef __nv_bfloat16 bf;
     if (smem > 48 * 1024) {
         if (smem > 200 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
         const void* fn = dt_bf16 ? (const void*)mu::ssd_scan_kernel<bf> : (const void*)mu::ssd_scan_kernel<float>;
         if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MU_ERR_LAUNCH;
     }
-    cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(n_seqs, n_heads), block(P * parts);
     return dt_bf16 ? mu::launch_pdl(mu::ssd_scan_kernel<bf>, grid, block, smem, s, 1, xbc, channels, (const bf*)dt_raw, lddt,
                                     dt_bias, a_log, skip, n_heads, P, N, groups, parts, seq_first, seq_slots, state,

@@ -115,8 +115,15 @@ class SandwichNormBlock(Arrangement):
         y = ctx.buffer("sublayer.out", tuple(x.shape), torch.float32)
         h = self._input(layer.norm1, x, ctx)
         ctx.note("ln1", h)
-        self._sublayer(layer.mixer, y, h, y, ctx, cache, owns_cache)
-        self._join(layer.extra["norm1b"], y, x, ctx)
+        pair = getattr(layer.mixer, "forward_pair", None)
+        if pair is not None and isinstance(layer.extra["norm1b"], RmsNorm):
+            # two mixers side by side: their weighted sum is made by the norm's launch as it reads them
+            first, second = pair(h, ctx, cache, owns_cache)
+            a, b = layer.mixer.scales
+            self._join(layer.extra["norm1b"], first, x, ctx, second=(a, second, b))
+        else:
+            self._sublayer(layer.mixer, y, h, y, ctx, cache, owns_cache)
+            self._join(layer.extra["norm1b"], y, x, ctx)
         ctx.note("res1", x)
         if not isinstance(layer.feed_forward, NoFeedForward):
             h = self._input(layer.norm2, x, ctx)
@@ -136,11 +143,11 @@ class SandwichNormBlock(Arrangement):
         return norm.forward(x)
 
     @staticmethod
-    def _join(norm, y, x, ctx) -> None:
+    def _join(norm, y, x, ctx, second=None) -> None:
         ctx.stream_copy = None
-        if isinstance(norm, RmsNorm) and norm.runtime.dtype == torch.bfloat16:
-            copy = ctx.buffer("stream.copy", tuple(x.shape), torch.bfloat16)
-            norm.add_into(y, x, copy=copy)
+        if isinstance(norm, RmsNorm):
+            copy = ctx.buffer("stream.copy", tuple(x.shape), torch.bfloat16) if norm.runtime.dtype == torch.bfloat16 else None
+            norm.add_into(y, x, copy=copy, second=second)
             ctx.stream_copy = copy
         else:
             norm.add_into(y, x)

@@ -111,7 +111,7 @@ class MappedAttention(Mixer):
         ops.mapped_attention(q, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq, self.n_heads,
                              self.n_kv_heads, self.maps, self.dim, self.vdim, self.scale, self.window, heads,
                              lam=self.lam, out_scale=self.out_scale, eps=self.eps, unit_rms=self.maps == 2,
-                             tiles=None if ctx.is_decode else ctx.q_tiles)
+                             tiles=None if ctx.is_decode else ctx.q_tiles, single_tokens=ctx.is_decode)
         ctx.note("attn", heads)
         self.out(heads, residual=residual if accumulate else None, out=residual)
 

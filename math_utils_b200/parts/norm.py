@@ -87,10 +87,11 @@ class RmsNorm(Norm):
     def forward_float(self, x, out=None):
         return self.runtime.ops.rms_norm_out(x, self.weight, self.eps, self.offset, self.scale, out=out)
 
-    def add_into(self, y, residual, copy=None) -> None:
-        """residual += norm(y); ``copy`` (bfloat16, shaped like the stream) receives the stream as it then is."""
+    def add_into(self, y, residual, copy=None, second=None) -> None:
+        """residual += norm(y); ``copy`` (bfloat16, shaped like the stream) receives the stream as it then is;
+        ``second`` = (a, y2, b): the norm's input is a * y + b * y2."""
         self.runtime.ops.rms_norm_out(y, self.weight, self.eps, self.offset, self.scale, out=residual, add=True,
-                                      copy=copy)
+                                      copy=copy, second=second)
 
 
 register_part("norm", "layer_norm", LayerNorm, replace=True)

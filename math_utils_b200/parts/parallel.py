@@ -21,6 +21,7 @@ class ParallelMixers(Mixer):
             raise ConfigError("parallel mixers: 'left' and 'right' are part specs")
         self.members = (build_part("mixer", left), build_part("mixer", right))
         self.scales = (float(self.param("left_scale")), float(self.param("right_scale")))
+        self.hidden_size = int(self.param("hidden_size"))
         self.graph_safe = all(m.graph_safe for m in self.members)
 
     def tensor_specs(self):
@@ -35,10 +36,16 @@ class ParallelMixers(Mixer):
             m.bind(tensors, runtime)
 
     def forward(self, h, residual, ctx, cache, owns_cache: bool, accumulate: bool = True) -> None:
+        outs = self.forward_pair(h, ctx, cache, owns_cache)
+        self.runtime.ops.scaled_sum(outs[0], self.scales[0], outs[1], self.scales[1], residual, add=accumulate)
+
+    def forward_pair(self, h, ctx, cache, owns_cache: bool):
+        """The two members' results, float32, not yet joined: for an arrangement whose next step (a norm of the
+        sum) can take them with their weights (``self.scales``) and save the pass that adds them."""
         tag = ctx.tag
         outs = []
         for name, member, view in zip(("left", "right"), self.members, cache or (None, None)):
-            y = ctx.buffer("parallel." + name, tuple(residual.shape), torch.float32)
+            y = ctx.buffer("parallel." + name, (ctx.n_tokens, self.hidden_size), torch.float32)
             ctx.tag = f"{tag}{name}."
             if member.can_overwrite:
                 member.forward(h, y, ctx, view, owns_cache, accumulate=False)
@@ -47,7 +54,7 @@ class ParallelMixers(Mixer):
                 member.forward(h, y, ctx, view, owns_cache)
             outs.append(y)
         ctx.tag = tag
-        self.runtime.ops.scaled_sum(outs[0], self.scales[0], outs[1], self.scales[1], residual, add=accumulate)
+        return outs
 
 
 register_part("mixer", "parallel", ParallelMixers, replace=True)

@@ -323,6 +323,17 @@ def test_output_norm_kernel():
         ops.rms_norm_out(dev(x), dev(w), eps, offset=1.0, scale=0.3, out=acc, add=True, copy=copy)
         assert np.abs(acc.cpu().numpy() - (stream + 0.3 * want)).max() < 3e-6
         assert (copy == acc.to(torch.bfloat16)).all()
+        # two branches that join with a weight each, summed by the same launch
+        x2 = rng.normal(0, 2, (9, 44))
+        acc = dev(stream)
+        ops.rms_norm_out(dev(x), dev(w), eps, offset=1.0, scale=0.3, out=acc, add=True, second=(0.6, dev(x2), 1.1))
+        want2 = plain.output_norm(0.6 * x + 1.1 * x2, {"n": w}, "n", eps)
+        assert np.abs(acc.cpu().numpy() - (stream + 0.3 * want2)).max() < 3e-6
+    # rows that are no whole 16-byte pieces, and rows longer than a block keeps in registers
+    for n in (45, 5000):
+        x, w = rng.normal(0, 3, (3, n)), rng.normal(0, 0.2, n)
+        want = plain.output_norm(x, {"n": w}, "n", 1e-5)
+        assert np.abs(ops.rms_norm_out(dev(x), dev(w), 1e-5, offset=1.0).cpu().numpy() - want).max() < 5e-6
 
 
 def test_gated_activation_and_weighted_sum_kernels():
@@ -347,7 +358,7 @@ def _paged(rng, lens, width, page=64):
     n_pages = sum(-(-n // page) for n in lens) + 3
     order = rng.permutation(n_pages)
     pages = np.zeros((n_pages, page, width))
-    table = np.zeros((len(lens), 8), dtype=np.int32)
+    table = np.zeros((len(lens), 24), dtype=np.int32)
     seqs, at = [], 0
     for s, n in enumerate(lens):
         rows = rng.normal(0, 1, (n, width))
@@ -418,7 +429,7 @@ def _plain_mapped(q, rows, pos, maps, dim, vdim, H, G, scale, window, lam, out_s
                                                       (4, 2, 1, 64, 32, 100), (8, 2, 2, 32, 64, 64), (2, 2, 2, 8, 200, 129)])
 def test_mapped_attention_kernel(dtype, H, G, maps, dim, vdim, window):
     ops, rng = _ops(), np.random.default_rng(5)
-    lens = [1, 2, 63, 64, 65, 300]
+    lens = [1, 2, 63, 64, 65, 300, 1400]
     width = G * (maps * dim + vdim)
     seqs, pages, table = _paged(rng, lens, width)
     scale, lam, out_scale, eps = 0.37, 0.45, 0.8, 1e-3
@@ -426,7 +437,7 @@ def test_mapped_attention_kernel(dtype, H, G, maps, dim, vdim, window):
         pages = dev(pages, dtype).float().cpu().numpy().astype(np.float64)
         seqs = [np.concatenate([pages[table[s, i]] for i in range(-(-n // 64))])[:n] for s, n in enumerate(lens)]
     # queries: the last position of every sequence, and some in the middle of the longest
-    picks = [(s, n - 1) for s, n in enumerate(lens)] + [(5, p) for p in (0, 63, 64, 127, 128, 191, 192, 250, 251)]
+    picks = [(s, n - 1) for s, n in enumerate(lens)] + [(5, p) for p in (0, 63, 64, 127, 128, 191, 192, 250, 251)] + [(6, 1100)]
     q = rng.normal(0, 1, (len(picks), H, maps, dim)) / math.sqrt(dim) * 3
     # Keys that stand out.  For the query at 299 of the long sequence: head 0's first map points at the oldest key
     # it sees (or a far one without a window), so that key's value must come through; the last head's first map
@@ -453,6 +464,14 @@ def test_mapped_attention_kernel(dtype, H, G, maps, dim, vdim, window):
     err = np.abs(got - want).max(axis=(1, 2))
     tol = 3e-5 if dtype == torch.float32 else 4e-2
     assert err.max() < tol, f"first wrong query {int(np.argmax(err > tol))}: {picks[int(np.argmax(err > tol))]}"
+    # the same queries through the kernel of single-token steps (pages shared out over blocks, then merged)
+    out.zero_()
+    ops.mapped_attention(dev(q.reshape(len(picks), -1), dtype), dev(pages, dtype), ints(table), 64,
+                         ints([p for _, p in picks]), ints([s for s, _ in picks]), H, G, maps, dim, vdim, scale, window, out,
+                         lam=lam, out_scale=out_scale, eps=eps, unit_rms=maps == 2, single_tokens=True)
+    got = out.float().cpu().numpy().reshape(len(picks), H, vdim)
+    err = np.abs(got - want).max(axis=(1, 2))
+    assert err.max() < tol, f"single tokens: first wrong query {int(np.argmax(err > tol))}: {picks[int(np.argmax(err > tol))]}"
 
 
 @pytest.mark.parametrize("H,G,maps,dim,vdim,window", [(4, 2, 2, 16, 16, 40), (2, 1, 2, 64, 128, 100), (8, 2, 1, 128, 64, 0),
@@ -504,7 +523,7 @@ def test_mapped_attention_on_tensor_cores_prompt_tiles(H, G, maps, dim, vdim, wi
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,P,N,groups,taps,parts", [(4, 8, 16, 2, 4, 1), (3, 5, 7, 1, 2, 3), (4, 32, 64, 2, 4, 2),
-                                                         (2, 64, 128, 1, 3, 1), (6, 16, 8, 3, 1, 2)])
+                                                         (2, 64, 128, 1, 3, 1), (6, 16, 8, 3, 1, 2), (2, 12, 200, 1, 2, 1)])
 def test_state_space_kernels(dtype, heads, P, N, groups, taps, parts):
     """Convolution, recurrence and gated norm against the plain mixer with identity matrices around them, a prompt
     cut into steps of several sizes for two sequences that share the steps."""
