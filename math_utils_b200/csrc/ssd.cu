@@ -127,8 +127,8 @@ __global__ void ssd_scan_kernel(const float* __restrict__ xbc, int channels, con
 }
 
 // The same recurrence with the state in registers: a block per (sequence, head, 8 columns of S); a half-warp owns
-// one column p and lane i of it the entries S[i + 16 k][p], so a step is NS fused multiply-adds for the update,
-// NS for the product with C and four shuffles, with no barrier.  B, C, x, dt and the decay of 16 steps at a time
+// one column p and lane i of it the entries S[i NS .. i NS + NS - 1][p], so a step is NS fused multiply-adds for the
+// update and NS for the product with C, with no barrier; the sums over a column's lanes are made 16 steps at a time.  B, C, x, dt and the decay of 16 steps at a time
 // come through shared memory in two stages (4-byte cp.async, so nothing has to be aligned), the next 16 steps on
 // their way while these are worked on.  N <= 16 * NS, NS up to 8 (larger states take the kernel above).
 constexpr int SC_STEPS = 16, SC_COLS = 8;
@@ -146,7 +146,7 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
                      const int* __restrict__ seq_slots, float* __restrict__ state, long long state_stride,
                      long long state_offset, float* __restrict__ y) {
     constexpr int NPAD = 16 * NS;
-    __shared__ float Bs[2][SC_STEPS][NPAD], Cs[2][SC_STEPS][NPAD], xs[2][SC_STEPS][SC_COLS], dts[2][SC_STEPS],
+    __shared__ __align__(16) float Bs[2][SC_STEPS][NPAD], Cs[2][SC_STEPS][NPAD], xs[2][SC_STEPS][SC_COLS], dts[2][SC_STEPS],
         decs[2][SC_STEPS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, part = lane & 15;
     const int pl = warp * 2 + (lane >> 4);
@@ -168,7 +168,7 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
     float S[NS];
 #pragma unroll
     for (int i = 0; i < NS; ++i) {
-        const int n = part + 16 * i;
+        const int n = part * NS + i;
         S[i] = (live && n < N) ? mine[(long long)n * P + p] : 0.0f;
     }
     const float rate = expf(a_log[h]), bias = dt_bias[h], d_skip = skip[h];
@@ -216,28 +216,57 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
         }
         __syncthreads();
         const int left = min(SC_STEPS, count - c * SC_STEPS);
-        for (int tt = 0; tt < left; ++tt) {
-            const float x = xs[buf][tt][pl], dt = dts[buf][tt], dec = decs[buf][tt];
-            const float dx = dt * x;
-            float acc = 0.0f;
+        // the 16 steps unrolled: a step's sum over the 16 lanes of a column is not made at once; each lane keeps its
+        // partial sum of every step, and at the end the 16 x 16 partial sums are added crosswise in 15 shuffles, after
+        // which lane i holds step i's sum.  So the only chain from step to step is the state's own.
+        float acc[SC_STEPS];
 #pragma unroll
-            for (int i = 0; i < NS; ++i) {
-                const float v = fmaf(dec, S[i], Bs[buf][tt][part + 16 * i] * dx);
-                S[i] = v;
-                acc = fmaf(v, Cs[buf][tt][part + 16 * i], acc);
+        for (int tt = 0; tt < SC_STEPS; ++tt) {
+            acc[tt] = 0.0f;
+            if (tt < left) {
+                const float dx = dts[buf][tt] * xs[buf][tt][pl], dec = decs[buf][tt];
+                const float* bp = &Bs[buf][tt][part * NS];
+                const float* cp = &Cs[buf][tt][part * NS];
+                float bv[NS], cv[NS];
+                if (NS % 4 == 0) {
+#pragma unroll
+                    for (int i = 0; i < NS; i += 4) {
+                        *reinterpret_cast<float4*>(bv + i) = *reinterpret_cast<const float4*>(bp + i);
+                        *reinterpret_cast<float4*>(cv + i) = *reinterpret_cast<const float4*>(cp + i);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < NS; ++i) {
+                        bv[i] = bp[i];
+                        cv[i] = cp[i];
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    const float v = fmaf(dec, S[i], bv[i] * dx);
+                    S[i] = v;
+                    acc[tt] = fmaf(v, cv[i], acc[tt]);
+                }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            if (part == 0 && live) y[(long long)(first + c * SC_STEPS + tt) * inner + h * P + p] = fmaf(d_skip, x, acc);
         }
+#pragma unroll
+        for (int width = 8; width >= 1; width >>= 1) {
+#pragma unroll
+            for (int k = 0; k < width; ++k) {
+                const bool upper = (part & width) != 0;
+                const float send = upper ? acc[k] : acc[k + width];
+                const float keep = upper ? acc[k + width] : acc[k];
+                acc[k] = keep + __shfl_xor_sync(0xffffffffu, send, width);
+            }
+        }
+        if (part < left && live)
+            y[(long long)(first + c * SC_STEPS + part) * inner + h * P + p] = fmaf(d_skip, xs[buf][part][pl], acc[0]);
         if (c + 1 < n_chunks) put_dt(next_raw, buf ^ 1);
         __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < NS; ++i) {
-        const int n = part + 16 * i;
+        const int n = part * NS + i;
         if (live && n < N) mine[(long long)n * P + p] = S[i];
     }
 }
