@@ -440,9 +440,9 @@ MU_EXPORT int mu_qk_prepare(void* q, long long ldq, const void* k, long long ldk
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 128;
     const size_t smem = ((size_t)(threads / 32) * dim + rot_dims) * sizeof(float);
-    // few tokens (single-token steps): a token's slices are spread over several blocks
+    // a token's slices are spread over several blocks, a warp a slice
     const int items = (n_heads + (k ? n_kv_heads : 0)) * maps;
-    const int shares = n_tokens >= 256 ? 1 : (items + 3) / 4;
+    const int shares = (items + 3) / 4;
     const dim3 grid(n_tokens, shares);
     typedef __nv_bfloat16 bf;
     if (is_bf16)

@@ -31,9 +31,8 @@ __global__ void ssd_conv_kernel(const TE* __restrict__ u, long long ldu, const f
                                 int move_tail, float* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long long)n_tokens * channels) return;
-    const int t = (int)(idx / channels), c = (int)(idx % channels);
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
     const int s = tok_seq[t];
     const int first = seq_first[s];
     float* tail = state + (long long)seq_slots[s] * state_stride;
@@ -133,9 +132,43 @@ __global__ void ssd_scan_kernel(const float* __restrict__ xbc, int channels, con
 // their way while these are worked on.  N <= 16 * NS, NS up to 8 (larger states take the kernel above).
 constexpr int SC_STEPS = 16, SC_COLS = 8;
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
                  : "memory");
+}
+
+// One step of a lane's NS state entries: S = dec S + B dx, and the lane's share of S . C (two running sums, so that
+// the additions of a step do not all wait for one another).
+template <int NS>
+__device__ __forceinline__ float scan_step(float (&S)[NS], const float* __restrict__ bp, const float* __restrict__ cp,
+                                           float dx, float dec) {
+    float sum0 = 0.0f, sum1 = 0.0f;
+    if (NS % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < NS; i += 4) {
+            const float4 b = *reinterpret_cast<const float4*>(bp + i);
+            const float4 c = *reinterpret_cast<const float4*>(cp + i);
+            S[i] = fmaf(dec, S[i], b.x * dx);
+            S[i + 1] = fmaf(dec, S[i + 1], b.y * dx);
+            S[i + 2] = fmaf(dec, S[i + 2], b.z * dx);
+            S[i + 3] = fmaf(dec, S[i + 3], b.w * dx);
+            sum0 = fmaf(S[i], c.x, sum0);
+            sum1 = fmaf(S[i + 1], c.y, sum1);
+            sum0 = fmaf(S[i + 2], c.z, sum0);
+            sum1 = fmaf(S[i + 3], c.w, sum1);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            S[i] = fmaf(dec, S[i], bp[i] * dx);
+            sum0 = fmaf(S[i], cp[i], sum0);
+        }
+    }
+    return sum0 + sum1;
 }
 
 template <typename TE, int NS>
@@ -174,18 +207,29 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
     const float rate = expf(a_log[h]), bias = dt_bias[h], d_skip = skip[h];
     const int n_chunks = (count + SC_STEPS - 1) / SC_STEPS;
 
+    // 16-byte copies where every piece of a row starts on such a boundary, 4-byte copies otherwise
+    const bool wide = channels % 4 == 0 && N % 4 == 0 && inner % 4 == 0 && ((uintptr_t)xbc & 15) == 0;
+    const int b_at = inner + g * N, c_at = inner + groups * N + g * N;
     auto issue = [&](int chunk, int buf) {
         const int left = min(SC_STEPS, count - chunk * SC_STEPS);
         const float* base = xbc + (long long)(first + chunk * SC_STEPS) * channels;
-        for (int i = tid; i < left * N; i += blockDim.x) {
-            const int tt = i / N, n = i % N;
+        for (int tt = 0; tt < left; ++tt) {
             const float* row = base + (long long)tt * channels;
-            cp_async4(&Bs[buf][tt][n], row + inner + g * N + n);
-            cp_async4(&Cs[buf][tt][n], row + inner + groups * N + g * N + n);
+            if (wide) {
+                for (int n = tid * 4; n < N; n += blockDim.x * 4) {
+                    cp_async16(&Bs[buf][tt][n], row + b_at + n);
+                    cp_async16(&Cs[buf][tt][n], row + c_at + n);
+                }
+            } else {
+                for (int n = tid; n < N; n += blockDim.x) {
+                    cp_async4(&Bs[buf][tt][n], row + b_at + n);
+                    cp_async4(&Cs[buf][tt][n], row + c_at + n);
+                }
+            }
         }
-        for (int i = tid; i < left * SC_COLS; i += blockDim.x) {
-            const int tt = i / SC_COLS, c = i % SC_COLS;
-            if (col0 + c < P) cp_async4(&xs[buf][tt][c], base + (long long)tt * channels + h * P + col0 + c);
+        {
+            const int tt = tid / SC_COLS, col = tid % SC_COLS;       // 128 threads: 16 steps x 8 columns
+            if (tt < left && col0 + col < P) cp_async4(&xs[buf][tt][col], base + (long long)tt * channels + h * P + col0 + col);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -220,33 +264,18 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
         // partial sum of every step, and at the end the 16 x 16 partial sums are added crosswise in 15 shuffles, after
         // which lane i holds step i's sum.  So the only chain from step to step is the state's own.
         float acc[SC_STEPS];
+        if (left == SC_STEPS) {                               // a whole chunk: no branch between the steps
 #pragma unroll
-        for (int tt = 0; tt < SC_STEPS; ++tt) {
-            acc[tt] = 0.0f;
-            if (tt < left) {
-                const float dx = dts[buf][tt] * xs[buf][tt][pl], dec = decs[buf][tt];
-                const float* bp = &Bs[buf][tt][part * NS];
-                const float* cp = &Cs[buf][tt][part * NS];
-                float bv[NS], cv[NS];
-                if (NS % 4 == 0) {
+            for (int tt = 0; tt < SC_STEPS; ++tt)
+                acc[tt] = scan_step<NS>(S, &Bs[buf][tt][part * NS], &Cs[buf][tt][part * NS], dts[buf][tt] * xs[buf][tt][pl],
+                                        decs[buf][tt]);
+        } else {
 #pragma unroll
-                    for (int i = 0; i < NS; i += 4) {
-                        *reinterpret_cast<float4*>(bv + i) = *reinterpret_cast<const float4*>(bp + i);
-                        *reinterpret_cast<float4*>(cv + i) = *reinterpret_cast<const float4*>(cp + i);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < NS; ++i) {
-                        bv[i] = bp[i];
-                        cv[i] = cp[i];
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < NS; ++i) {
-                    const float v = fmaf(dec, S[i], bv[i] * dx);
-                    S[i] = v;
-                    acc[tt] = fmaf(v, cv[i], acc[tt]);
-                }
+            for (int tt = 0; tt < SC_STEPS; ++tt) {
+                acc[tt] = 0.0f;
+                if (tt < left)
+                    acc[tt] = scan_step<NS>(S, &Bs[buf][tt][part * NS], &Cs[buf][tt][part * NS],
+                                            dts[buf][tt] * xs[buf][tt][pl], decs[buf][tt]);
             }
         }
 #pragma unroll
@@ -271,26 +300,40 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
     }
 }
 
+constexpr int GN_KEEP = 8;       // gated values a thread keeps between the statistics and the output
+
 template <typename TE>
-__global__ void gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __restrict__ z, long long ldz,
-                                        const float* __restrict__ weight, int width, float eps, TE* __restrict__ out,
-                                        long long ldo) {
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __restrict__ z, long long ldz,
+                        const float* __restrict__ weight, int width, float eps, TE* __restrict__ out, long long ldo) {
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, part = blockIdx.y;
     const float* ys = y + (long long)t * ldy + (long long)part * width;
     const TE* zs = z + (long long)t * ldz + (long long)part * width;
+    float kept[GN_KEEP];
     float sq = 0.0f;
-    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+#pragma unroll
+    for (int i = 0; i < GN_KEEP; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+        kept[i] = d < width ? ys[d] * silu_f(to_float(zs[d])) : 0.0f;
+        sq += kept[i] * kept[i];
+    }
+    for (int d = threadIdx.x + GN_KEEP * blockDim.x; d < width; d += blockDim.x) {
         const float v = ys[d] * silu_f(to_float(zs[d]));
         sq += v * v;
     }
     const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
-    for (int d = threadIdx.x; d < width; d += blockDim.x) {
-        const float v = ys[d] * silu_f(to_float(zs[d]));
-        out[(long long)t * ldo + (long long)part * width + d] = from_float<TE>(v * inv * weight[(long long)part * width + d]);
+    TE* dst = out + (long long)t * ldo + (long long)part * width;
+    const float* w = weight + (long long)part * width;
+#pragma unroll
+    for (int i = 0; i < GN_KEEP; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+        if (d < width) dst[d] = from_float<TE>(kept[i] * inv * w[d]);
     }
+    for (int d = threadIdx.x + GN_KEEP * blockDim.x; d < width; d += blockDim.x)
+        dst[d] = from_float<TE>(ys[d] * silu_f(to_float(zs[d])) * inv * w[d]);
 }
 
 }  // namespace mu
@@ -306,8 +349,7 @@ MU_EXPORT int mu_ssd_conv(const void* u, long long ldu, int u_bf16, const float*
         return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
-    const long long total = (long long)n_tokens * channels;
-    const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+    const dim3 grid(n_tokens, (channels + 255) / 256), block(256);
     int code = u_bf16 ? mu::launch_pdl(mu::ssd_conv_kernel<bf>, grid, block, 0, s, 1, (const bf*)u, ldu, weight, bias,
                                        channels, taps, n_tokens, tok_seq, seq_first, seq_slots, state, state_stride,
                                        single_tokens, out)
