@@ -17,7 +17,9 @@ import torch
 STAGE_NAMES = OrderedDict([
     ("embed", "embedding"), ("ln1", "norm 1"), ("qkv", "q | k | v product"),
     ("proj", "queries | gate | latent product"), ("q_latent", "cache append, queries into latent space, rotation"),
-    ("mixed", "attention over latent rows"), ("attn", "attention"),
+    ("mixed", "attention over latent rows"),
+    ("q", "q | k | v product, query/key norm, rotation, cache append"),
+    ("scan", "state-space input product, convolution, scan"), ("attn", "attention / gated norm of the scan"),
     ("res1", "output projection"), ("ln2", "norm 2"), ("route", "router and grouping"), ("act", "feed-forward up"), ("res2", "feed-forward down"),
     ("lnf", "final norm"), ("logits", "output head"),
 ])
