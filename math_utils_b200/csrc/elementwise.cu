@@ -36,7 +36,8 @@ template <typename TW>
 __global__ void embed_pair_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const int* __restrict__ tok_seq,
                                   const int* __restrict__ seq_slots, int* __restrict__ last_token,
                                   const TW* __restrict__ table, const TW* __restrict__ pair_table, float* __restrict__ x,
-                                  int hidden, int buckets, long long mul_prev, long long mul_cur, int remember) {
+                                  __nv_bfloat16* __restrict__ copy, int hidden, int buckets, long long mul_prev,
+                                  long long mul_cur, int remember) {
     __shared__ long long pair_row;
     pdl_trigger();
     pdl_wait();
@@ -58,7 +59,11 @@ __global__ void embed_pair_kernel(const int* __restrict__ ids, const int* __rest
     const TW* psrc = pair_table + pair_row * hidden;
     float* dst = x + (long long)t * hidden;
 #pragma unroll 4
-    for (int d = threadIdx.x; d < hidden; d += blockDim.x) dst[d] = to_float(src[d]) + to_float(psrc[d]);
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        const float v = to_float(src[d]) + to_float(psrc[d]);
+        dst[d] = v;
+        if (copy) copy[(long long)t * hidden + d] = __float2bfloat16_rn(v);    // the first sublayer's input
+    }
 }
 
 __global__ void remember_tokens_kernel(const int* __restrict__ ids, const int* __restrict__ seq_first,
@@ -198,8 +203,9 @@ MU_EXPORT int mu_embed(const int* ids, const int* pos, const void* table, const 
 }
 
 // Token rows plus hashed rows of (token before, token); single_tokens: every sequence brings one token.
+// copy (optional, bfloat16 [n_tokens][hidden]): the same rows rounded, for a first sublayer that reads the stream itself.
 MU_EXPORT int mu_embed_pair(const int* ids, const int* pos, const int* tok_seq, const int* seq_first, const int* seq_slots,
-                            int* last_token, const void* table, const void* pair_table, float* x, int n_tokens, int n_seqs,
+                            int* last_token, const void* table, const void* pair_table, float* x, void* copy, int n_tokens, int n_seqs,
                             int hidden, int buckets, long long mul_prev, long long mul_cur, int table_bf16,
                             int single_tokens, void* stream) {
     if (n_tokens <= 0) return MU_OK;
@@ -211,10 +217,11 @@ MU_EXPORT int mu_embed_pair(const int* ids, const int* pos, const int* tok_seq, 
     const int code =
         table_bf16 ? mu::launch_pdl(mu::embed_pair_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
                                     tok_seq, seq_slots, last_token, (const __nv_bfloat16*)table,
-                                    (const __nv_bfloat16*)pair_table, x, hidden, buckets, mul_prev, mul_cur, single_tokens)
+                                    (const __nv_bfloat16*)pair_table, x, (__nv_bfloat16*)copy, hidden, buckets, mul_prev,
+                                    mul_cur, single_tokens)
                    : mu::launch_pdl(mu::embed_pair_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos, tok_seq,
-                                    seq_slots, last_token, (const float*)table, (const float*)pair_table, x, hidden,
-                                    buckets, mul_prev, mul_cur, single_tokens);
+                                    seq_slots, last_token, (const float*)table, (const float*)pair_table, x,
+                                    (__nv_bfloat16*)copy, hidden, buckets, mul_prev, mul_cur, single_tokens);
     if (code != MU_OK || single_tokens) return code;
     return mu::launch_pdl(mu::remember_tokens_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, 1, ids, seq_first,
                           seq_slots, last_token, n_seqs);

@@ -85,8 +85,8 @@ _SIGNATURES = {
                             _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
                                _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p],
-    "mu_embed_pair": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
-                      _c_int, _c_int, _c_p],
+    "mu_embed_pair": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll,
+                      _c_ll, _c_int, _c_int, _c_p],
     "mu_rms_norm_out": [_c_p, _c_ll, _c_p, _c_ll, _c_f, _c_f, _c_p, _c_p, _c_f, _c_f, _c_f, _c_p, _c_ll, _c_int, _c_int,
                         _c_p, _c_ll, _c_int, _c_int, _c_p],
     "mu_gated_act": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p],
@@ -106,7 +106,7 @@ _SIGNATURES = {
     "mu_ssd_conv": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll,
                     _c_int, _c_p, _c_p],
     "mu_ssd_scan": [_c_p, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
-                    _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p],
+                    _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_int, _c_p],
     "mu_gated_group_norm": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_ll, _c_int, _c_p],
     "mu_dynamic_tanh": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_rms_norm": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p],
@@ -410,11 +410,16 @@ def scaled_sum(p: torch.Tensor, a: float, q: torch.Tensor, b: float, out: torch.
 
 def embed_pair(ids: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor, seq_first: torch.Tensor,
                seq_slots: torch.Tensor, last_token: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor,
-               mul_prev: int, mul_cur: int, single_tokens: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               mul_prev: int, mul_cur: int, single_tokens: bool, out: Optional[torch.Tensor] = None,
+               copy: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = table[ids[t]] + pair_table[(previous * mul_prev + ids[t] * mul_cur) mod buckets] as float32, with
     buckets = pair_table's rows - 1 and that last row for a sequence's first token.  The token before the step's
-    first token of a sequence is ``last_token[slot]``, which is then set to the sequence's last token of the step."""
-    _need_cuda(ids, positions, tok_seq, seq_first, seq_slots, last_token, table, pair_table, out)
+    first token of a sequence is ``last_token[slot]``, which is then set to the sequence's last token of the step.
+    ``copy`` (contiguous bfloat16 [T, hidden]) receives the same rows rounded."""
+    _need_cuda(ids, positions, tok_seq, seq_first, seq_slots, last_token, table, pair_table, out, copy)
+    if copy is not None and (copy.dtype != torch.bfloat16 or not copy.is_contiguous()
+                             or tuple(copy.shape) != (ids.numel(), table.shape[1])):
+        raise KernelError("embed_pair: the copy is contiguous bfloat16 [T, hidden]")
     for t, name in ((ids, "ids"), (positions, "positions"), (tok_seq, "tok_seq"), (seq_first, "seq_first"),
                     (seq_slots, "seq_slots"), (last_token, "last_token")):
         _i32(t, name)
@@ -425,7 +430,7 @@ def embed_pair(ids: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _check(library().mu_embed_pair(_ptr(ids), _ptr(positions), _ptr(tok_seq), _ptr(seq_first), _ptr(seq_slots),
-                                   _ptr(last_token), _ptr(table), _ptr(pair_table), _ptr(out), n, seq_slots.numel(),
+                                   _ptr(last_token), _ptr(table), _ptr(pair_table), _ptr(out), _ptr(copy), n, seq_slots.numel(),
                                    hidden, pair_table.shape[0] - 1, int(mul_prev), int(mul_cur), _is_bf16(table),
                                    int(single_tokens), _stream()), "embed_pair", launches=1 if single_tokens else 2)
     return out
@@ -552,7 +557,7 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias, a_log, skip, n_he
     _check(library().mu_ssd_scan(_ptr(xbc), xbc.shape[1], _ptr(dt_raw), dt_raw.stride(0), _is_bf16(dt_raw), _ptr(dt_bias),
                                  _ptr(a_log), _ptr(skip), seq_slots.numel(), int(n_heads), int(head_dim), int(n_state),
                                  int(groups), _ptr(seq_first), _ptr(seq_slots), _ptr(state), state.stride(0),
-                                 int(state_offset), _ptr(out), _stream()),
+                                 int(state_offset), _ptr(out), int(xbc.shape[0] > 4 * seq_slots.numel()), _stream()),
            ("ssd_scan(heads={}, P={}, N={})", n_heads, head_dim, n_state))
     return out
 

@@ -125,12 +125,13 @@ __global__ void ssd_scan_kernel(const float* __restrict__ xbc, int channels, con
     for (int e = tid; e < N * P; e += blockDim.x) mine[e] = S[e];
 }
 
-// The same recurrence with the state in registers: a block per (sequence, head, 8 columns of S); a half-warp owns
-// one column p and lane i of it the entries S[i NS .. i NS + NS - 1][p], so a step is NS fused multiply-adds for the
-// update and NS for the product with C, with no barrier; the sums over a column's lanes are made 16 steps at a time.  B, C, x, dt and the decay of 16 steps at a time
-// come through shared memory in two stages (4-byte cp.async, so nothing has to be aligned), the next 16 steps on
-// their way while these are worked on.  N <= 16 * NS, NS up to 8 (larger states take the kernel above).
-constexpr int SC_STEPS = 16, SC_COLS = 8;
+// The same recurrence with the state in registers: a block per (sequence, head, a few columns of S); LPC lanes own
+// one column p, lane i of them the entries S[i NS .. i NS + NS - 1][p], so a step is NS fused multiply-adds for the
+// update and NS for the product with C, with no barrier; the sums over a column's lanes are made 16 steps at a time.
+// B, C, x, dt and the decay of 16 steps at a time come through shared memory in two stages (cp.async, 4 bytes a copy
+// where 16 would not be aligned), the next 16 steps on their way while these are worked on.  N <= LPC * NS <= 128
+// (larger states take the kernel above).
+constexpr int SC_STEPS = 16;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
@@ -171,18 +172,21 @@ __device__ __forceinline__ float scan_step(float (&S)[NS], const float* __restri
     return sum0 + sum1;
 }
 
-template <typename TE, int NS>
+// LPC: lanes that share a column of S (16: a warp takes two columns; 32: one, which doubles the warps a step of a
+// given size keeps busy).
+template <typename TE, int NS, int LPC>
 __global__ void __launch_bounds__(128)
 ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __restrict__ dt_raw, long long lddt,
                      const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ skip,
                      int n_heads, int P, int N, int groups, const int* __restrict__ seq_first,
                      const int* __restrict__ seq_slots, float* __restrict__ state, long long state_stride,
                      long long state_offset, float* __restrict__ y) {
-    constexpr int NPAD = 16 * NS;
+    constexpr int NPAD = LPC * NS;
+    constexpr int SC_COLS = 4 * (32 / LPC);                  // columns of a block: four warps
     __shared__ __align__(16) float Bs[2][SC_STEPS][NPAD], Cs[2][SC_STEPS][NPAD], xs[2][SC_STEPS][SC_COLS], dts[2][SC_STEPS],
         decs[2][SC_STEPS];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, part = lane & 15;
-    const int pl = warp * 2 + (lane >> 4);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, part = lane % LPC;
+    const int pl = warp * (32 / LPC) + lane / LPC;
     for (int i = tid; i < 2 * SC_STEPS * NPAD; i += blockDim.x) {
         (&Bs[0][0][0])[i] = 0.0f;
         (&Cs[0][0][0])[i] = 0.0f;
@@ -228,8 +232,8 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
             }
         }
         {
-            const int tt = tid / SC_COLS, col = tid % SC_COLS;       // 128 threads: 16 steps x 8 columns
-            if (tt < left && col0 + col < P) cp_async4(&xs[buf][tt][col], base + (long long)tt * channels + h * P + col0 + col);
+            const int tt = tid / SC_COLS, col = tid % SC_COLS;       // 16 steps x the block's columns
+            if (tt < left && tt < SC_STEPS && col0 + col < P) cp_async4(&xs[buf][tt][col], base + (long long)tt * channels + h * P + col0 + col);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -278,6 +282,10 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
                                             dts[buf][tt] * xs[buf][tt][pl], decs[buf][tt]);
             }
         }
+        if (LPC == 32) {
+#pragma unroll
+            for (int k = 0; k < SC_STEPS; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 16);
+        }
 #pragma unroll
         for (int width = 8; width >= 1; width >>= 1) {
 #pragma unroll
@@ -288,7 +296,7 @@ ssd_scan_cols_kernel(const float* __restrict__ xbc, int channels, const TE* __re
                 acc[k] = keep + __shfl_xor_sync(0xffffffffu, send, width);
             }
         }
-        if (part < left && live)
+        if (part < left && live)                              // (part < 16: with 32 lanes a column both halves hold the sums)
             y[(long long)(first + c * SC_STEPS + part) * inner + h * P + p] = fmaf(d_skip, xs[buf][part][pl], acc[0]);
         if (c + 1 < n_chunks) put_dt(next_raw, buf ^ 1);
         __syncthreads();
@@ -368,7 +376,7 @@ MU_EXPORT int mu_ssd_conv(const void* u, long long ldu, int u_bf16, const float*
 MU_EXPORT int mu_ssd_scan(const float* xbc, int channels, const void* dt_raw, long long lddt, int dt_bf16,
                           const float* dt_bias, const float* a_log, const float* skip, int n_seqs, int n_heads, int P,
                           int N, int groups, const int* seq_first, const int* seq_slots, float* state,
-                          long long state_stride, long long state_offset, float* y, void* stream) {
+                          long long state_stride, long long state_offset, float* y, int long_steps, void* stream) {
     if (n_seqs <= 0) return MU_OK;
     if (!xbc || !dt_raw || !dt_bias || !a_log || !skip || !seq_first || !seq_slots || !state || !y || n_heads <= 0 ||
         P <= 0 || N <= 0 || groups <= 0 || n_heads % groups)
@@ -376,18 +384,22 @@ MU_EXPORT int mu_ssd_scan(const float* xbc, int channels, const void* dt_raw, lo
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
     if (N <= 128) {                                   // the state in registers, 8 columns of S a block
-        const dim3 grid(n_seqs, n_heads, (P + mu::SC_COLS - 1) / mu::SC_COLS), block(128);
-#define MU_SCAN_COLS(NS)                                                                                               \
-    return dt_bf16 ? mu::launch_pdl(mu::ssd_scan_cols_kernel<bf, NS>, grid, block, 0, s, 1, xbc, channels,             \
-                                    (const bf*)dt_raw, lddt, dt_bias, a_log, skip, n_heads, P, N, groups, seq_first,   \
-                                    seq_slots, state, state_stride, state_offset, y)                                   \
-                   : mu::launch_pdl(mu::ssd_scan_cols_kernel<float, NS>, grid, block, 0, s, 1, xbc, channels,          \
-                                    (const float*)dt_raw, lddt, dt_bias, a_log, skip, n_heads, P, N, groups,           \
-                                    seq_first, seq_slots, state, state_stride, state_offset, y)
-        if (N <= 16) MU_SCAN_COLS(1);
-        if (N <= 32) MU_SCAN_COLS(2);
-        if (N <= 64) MU_SCAN_COLS(4);
-        MU_SCAN_COLS(8);
+        const dim3 block(128);
+#define MU_SCAN_COLS(NS, LPC)                                                                                          \
+    do {                                                                                                               \
+        const dim3 grid(n_seqs, n_heads, (P + 4 * (32 / LPC) - 1) / (4 * (32 / LPC)));                                 \
+        return dt_bf16 ? mu::launch_pdl(mu::ssd_scan_cols_kernel<bf, NS, LPC>, grid, block, 0, s, 1, xbc, channels,    \
+                                        (const bf*)dt_raw, lddt, dt_bias, a_log, skip, n_heads, P, N, groups,          \
+                                        seq_first, seq_slots, state, state_stride, state_offset, y)                    \
+                       : mu::launch_pdl(mu::ssd_scan_cols_kernel<float, NS, LPC>, grid, block, 0, s, 1, xbc, channels, \
+                                        (const float*)dt_raw, lddt, dt_bias, a_log, skip, n_heads, P, N, groups,       \
+                                        seq_first, seq_slots, state, state_stride, state_offset, y);                   \
+    } while (0)
+        if (N <= 16) MU_SCAN_COLS(1, 16);
+        if (N <= 32) MU_SCAN_COLS(2, 16);
+        if (N <= 64) MU_SCAN_COLS(4, 16);
+        if (!long_steps) MU_SCAN_COLS(8, 16);         // a few tokens a sequence: fewer, larger blocks
+        MU_SCAN_COLS(4, 32);                          // 65 .. 128 over many tokens: a warp a column, twice the warps
 #undef MU_SCAN_COLS
     }
     if (P > 1024) return MU_ERR_UNSUPPORTED_SIZE;

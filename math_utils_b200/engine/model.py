@@ -124,6 +124,7 @@ class DecoderModel:
         x = a.embedding.forward(ctx, a.position.embedding_table())
         if a.embedding_norm is not None:
             x = a.embedding_norm.forward_float(x, out=x)
+            ctx.stream_copy = None
         ctx.note("embed", x)
         for i, entry in enumerate(self.plan.schedule):
             layer = a.layers[entry.layer]

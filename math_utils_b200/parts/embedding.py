@@ -61,9 +61,15 @@ class TokenPairEmbedding(Embedding):
             raise ValueError("the token-pair embedding adds no position table")
         if ctx.last_tokens is None or ctx.seq_first is None:
             raise ValueError("the token-pair embedding needs the cache's last tokens and the step's sequence starts")
-        return self.runtime.ops.embed_pair(ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_first, ctx.seq_slots,
-                                           ctx.last_tokens, self.weight, self.pair_weight, self.mul_prev, self.mul_cur,
-                                           ctx.is_decode)
+        import torch
+        # in bfloat16 the same launch leaves the rows rounded too, for a first sublayer that reads the stream itself
+        copy = (ctx.buffer("stream.copy", (ctx.n_tokens, self.hidden_size), torch.bfloat16)
+                if self.runtime.dtype == torch.bfloat16 else None)
+        x = self.runtime.ops.embed_pair(ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_first, ctx.seq_slots,
+                                        ctx.last_tokens, self.weight, self.pair_weight, self.mul_prev, self.mul_cur,
+                                        ctx.is_decode, copy=copy)
+        ctx.stream_copy = copy
+        return x
 
 
 class TiedHead(Head):
