@@ -256,6 +256,23 @@ def test_greedy_generation_through_the_library(folders, name):
     assert eager == outs[0], "eager steps and replayed steps generate different tokens"
 
 
+def test_requests_that_end_early_leave_the_others_alone(folders):
+    """A stop token ends some requests early: the batch thins out, the rest moves to a smaller recorded step (whose
+    set-up run must not move recurrent state or the last token on), and nobody's tokens change."""
+    llm = LLM(folders["a"], dtype="float32", temperature=0.0, max_tokens=30, context=512)
+    prompts = [tokens_for("a", n, seed=70 + n) for n in (40, 9, 66, 3, 21)]
+    free = llm.generate(prompts, stop_ids=[])
+    # a token that request 0 produces early and request 2 later, if there is one; else request 0's sixth token
+    stop = free[0][5]
+    want = []
+    for out in free:
+        want.append(out[:out.index(stop)] if stop in out else out)
+    assert len(want[0]) <= 5 and any(len(w) == 30 for w in want), "the test's premise: some end early, some run on"
+    got = llm.generate(prompts, stop_ids=[stop])
+    assert got == want
+    assert llm.generate(prompts[1:], stop_ids=[stop]) == want[1:]
+
+
 def test_conversation_on_a_kept_slot(folders):
     """Two turns through ``LLM.prompt``: the slot keeps keys, values, the recurrence's state and the last token."""
     llm = LLM(folders["a"], dtype="float32", temperature=0.0, max_tokens=9, context=512)
