@@ -493,12 +493,12 @@ def lusalorn_config(size):
     state-space mixer; and the GPT-2 configuration of equal width, layer count, vocabulary and feed-forward work per
     token (a gated feed-forward has three matrices where GPT-2's has two), head size 64."""
     D, (H, G, d, dv, window), (lh, lg, ld, lv), (sh, sp, sn), ff, L = LUSALORN_SIZES[size]
-    windowed = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "mask": {"size": window}, "scale": d ** -0.5, "diff": 0.3,
-                "rot": {"base": 250000.0, "dims": d // 2}}
+    windowed = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "mask": {"size": window}, "scale": d ** -0.5, "diff": 0.2,
+                "rot": {"base": 500000.0, "dims": d // 2}}
     both = {"left": {"heads": lh, "kv_heads": lg, "dim": ld, "vdim": lv, "scale": ld ** -0.5,
-                     "rot": {"base": 1.0e6, "dims": ld, "scaling": {"factor": 8.0, "original": 512, "fast": 32.0, "slow": 1.0}}},
+                     "rot": {"base": 2.0e6, "dims": ld, "scaling": {"factor": 4.0, "original": 1024, "fast": 16.0, "slow": 2.0}}},
             "right": {"heads": sh, "vdim": sp, "state": sn, "groups": 1, "conv": 4, "norm_groups": 1},
-            "left_scale": 0.6, "right_scale": 1.1}
+            "left_scale": 0.7, "right_scale": 1.2}
     mlp = {"kind": "dense", "ff": ff}
     layers = []
     for i in range(L):
@@ -506,8 +506,8 @@ def lusalorn_config(size):
             layers.append({"type": "attention", "mixer": dict(windowed, **({"kv_from": 0} if i else {})), "mlp": mlp})
         else:
             layers.append({"type": "parallel", "mixer": both, "mlp": mlp})
-    ours = {"architecture": "Lusalorn", "vocab": FAMILY_VOCAB, "width": D, "residual_mult": 0.3, "norm": {"eps": 1e-6},
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+    ours = {"architecture": "Lusalorn", "vocab": FAMILY_VOCAB, "width": D, "residual_mult": 0.25, "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 131}}, "layers": layers}
     twin = {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "n_layer": L, "n_embd": D, "n_head": D // 64,
             "n_inner": ff * 3 // 2, "vocab_size": FAMILY_VOCAB, "n_positions": CONTEXT,
             "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new"}
