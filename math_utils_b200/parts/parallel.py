@@ -22,6 +22,7 @@ class ParallelMixers(Mixer):
         self.members = (build_part("mixer", left), build_part("mixer", right))
         self.scales = (float(self.param("left_scale")), float(self.param("right_scale")))
         self.hidden_size = int(self.param("hidden_size"))
+        self._side = None
         self.graph_safe = all(m.graph_safe for m in self.members)
 
     def tensor_specs(self):
@@ -39,20 +40,45 @@ class ParallelMixers(Mixer):
         outs = self.forward_pair(h, ctx, cache, owns_cache)
         self.runtime.ops.scaled_sum(outs[0], self.scales[0], outs[1], self.scales[1], residual, add=accumulate)
 
+    # Steps of up to this many tokens (single-token steps above all) run the second member on a stream of its own
+    # beside the first: both are short chains of dependent launches, and side by side the layer's chain is as long
+    # as the longer of the two.  (At this size every product is a kernel that keeps no workspace in device memory
+    # that two launches could share.)  Larger steps fill the device a member at a time and run one after the other.
+    SIDE_BY_SIDE_TOKENS = 32
+
     def forward_pair(self, h, ctx, cache, owns_cache: bool):
         """The two members' results, float32, not yet joined: for an arrangement whose next step (a norm of the
         sum) can take them with their weights (``self.scales``) and save the pass that adds them."""
         tag = ctx.tag
-        outs = []
-        for name, member, view in zip(("left", "right"), self.members, cache or (None, None)):
-            y = ctx.buffer("parallel." + name, (ctx.n_tokens, self.hidden_size), torch.float32)
+        views = cache or (None, None)
+        outs = [ctx.buffer("parallel." + name, (ctx.n_tokens, self.hidden_size), torch.float32) for name in ("left", "right")]
+
+        def run(i, name):
             ctx.tag = f"{tag}{name}."
+            member = self.members[i]
             if member.can_overwrite:
-                member.forward(h, y, ctx, view, owns_cache, accumulate=False)
+                member.forward(h, outs[i], ctx, views[i], owns_cache, accumulate=False)
             else:
-                y.zero_()
-                member.forward(h, y, ctx, view, owns_cache)
-            outs.append(y)
+                outs[i].zero_()
+                member.forward(h, outs[i], ctx, views[i], owns_cache)
+
+        # (two members of one kind would share that kind's scratch memory: they run one after the other)
+        apart = type(self.members[0]) is not type(self.members[1])
+        if apart and ctx.trace is None and ctx.n_tokens <= self.SIDE_BY_SIDE_TOKENS and h.is_cuda:
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=h.device)
+                self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+            self._fork.record(main)
+            self._side.wait_event(self._fork)               # the input is ready
+            with torch.cuda.stream(self._side):
+                run(1, "right")
+                self._join.record(self._side)
+            run(0, "left")
+            main.wait_event(self._join)                     # both results are there for what comes next
+        else:
+            run(0, "left")
+            run(1, "right")
         ctx.tag = tag
         return outs
 
